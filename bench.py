@@ -1,0 +1,441 @@
+"""Benchmark of the MoE expert hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl ours|reference]
+
+Workload (`config.workload`): the decode sweep configuration -- a stack of 8 MoE
+layers, hidden 4096, 128 experts, top-8 softmax routing, expert FFN dim 1536,
+gate/up weights Q2_K and down weights Q3_K (random super-blocks), T tokens of
+N(0,1) activations per layer.  One "step" is one pass of T tokens through the 8
+layers: router top-k, grouping, gate/up matmul + SwiGLU, down matmul, weighted
+combine.  Weights of the 8 layers (7 GB) cycle through HBM every step, so the
+inputs are far larger than L2.
+
+Printed JSON (rank 0): `value` = tokens/s with inputs resident in HBM; `e2e` =
+the same through the host-buffer entry (pinned host -> device copy of the
+activations and device -> host read of the output inside the timed region, per
+layer, as the reference's layer call does); `roofline` = achieved HBM GB/s of
+the dominant kernel (gate/up matmul) against the measured copy bandwidth;
+`cpu_baseline` = the CPU restatement of the reference path timed on this box.
+
+With N > 1 (torchrun) the experts of every layer are sharded over the ranks
+(expert parallel); every rank brings its own T tokens (weak scaling), token
+rows are exchanged with NCCL collectives.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D, F, E, K, LAYERS = 4096, 1536, 128, 8, 8
+Q2_K, Q3_K = 10, 11
+TYPES = (Q2_K, Q2_K, Q3_K)
+RB_GU = D // 256 * 84      # bytes per gate / up row
+RB_DN = F // 256 * 110     # bytes per down row
+METRIC = "moe_layer_stack_decode_tokens_per_s"
+UNIT = "tokens/s"
+HALF_OFFS = {Q2_K: (80, 82), Q3_K: (108,)}
+BB = {Q2_K: 84, Q3_K: 110}
+
+
+def workload_name(T):
+    return ("decode sweep: 8 MoE layers, hidden 4096, 128 experts top-8 softmax, ffn 1536, "
+            "gate/up Q2_K + down Q3_K random blocks, batch %d tokens" % T)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# synthetic weights
+# ---------------------------------------------------------------------------
+def torch_blocks(qtype, n_blocks, gen, device):
+    """uint8 [n_blocks, block_bytes]: uniform random bytes, fp16 super-scales |N(0, 0.01)|"""
+    import torch
+    bb = BB[qtype]
+    blocks = torch.randint(0, 256, (n_blocks, bb), dtype=torch.uint8, device=device, generator=gen)
+    for off in HALF_OFFS[qtype]:
+        h = (torch.randn(n_blocks, device=device, generator=gen) * 0.01).abs().to(torch.float16)
+        blocks[:, off:off + 2] = h.view(torch.uint8).reshape(n_blocks, 2)
+    return blocks
+
+
+def make_layer_weights(seed, layer, device, e_lo=0, e_hi=E):
+    """weights of experts [e_lo, e_hi) of one layer; every expert has its own generator
+    stream so that any shard sees the same bytes"""
+    import torch
+    ne = e_hi - e_lo
+    wg = torch.empty((ne, F, RB_GU), dtype=torch.uint8, device=device)
+    wu = torch.empty((ne, F, RB_GU), dtype=torch.uint8, device=device)
+    wd = torch.empty((ne, D, RB_DN), dtype=torch.uint8, device=device)
+    gen = torch.Generator(device=device)
+    for e in range(e_lo, e_hi):
+        gen.manual_seed(seed * 1000003 + layer * 1009 + e)
+        wg[e - e_lo] = torch_blocks(Q2_K, F * (D // 256), gen, device).reshape(F, RB_GU)
+        wu[e - e_lo] = torch_blocks(Q2_K, F * (D // 256), gen, device).reshape(F, RB_GU)
+        wd[e - e_lo] = torch_blocks(Q3_K, D * (F // 256), gen, device).reshape(D, RB_DN)
+    gen.manual_seed(seed * 7919 + layer)
+    wr = torch.randn((E, D), device=device, generator=gen) * 0.02
+    return wg, wu, wd, wr
+
+
+def make_inputs(seed, T, device, rank=0):
+    import torch
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 31 + 17 + 1000 * rank)
+    return [torch.randn((T, D), device=device, generator=gen) for _ in range(LAYERS)]
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows = []
+        self.proc = None
+        self.idx = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+                for n, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except (ValueError, IndexError):
+                pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# CPU leg (the oracle's AVX2 + OpenMP twin); used by --impl reference and by cpu_baseline
+# ---------------------------------------------------------------------------
+def cpu_layer_runner(wg, wu, wd, wr):
+    """returns f(x) -> out running router + expert FFN of one layer on the host cores"""
+    from oracle import oracle as O
+    L = O.make_layer(D, F, E, K, TYPES, wg, wu, wd)
+
+    def run(x, threads=0):
+        logits = O.router_logits(x, wr)
+        _, ids, w, _ = O.router_select(logits, K)
+        out, used = O.moe_ffn(L, x, ids, w, fast=True, threads=threads)
+        return out, used
+    return run
+
+
+def run_reference_arm(args, rank, world):
+    """the CPU restatement of the reference's ggml path on this box's host cores"""
+    if rank != 0:
+        return
+    import torch
+    cores = os.cpu_count() or 1
+    T = args.tokens
+    # bounded sample: the first `nl` layers of the stack, scaled to 8 layers
+    nl = 2
+    layers = []
+    for l in range(nl):
+        wg, wu, wd, wr = make_layer_weights(args.seed, l, "cpu")
+        layers.append(cpu_layer_runner(wg.numpy(), wu.numpy(), wd.numpy(), wr.numpy()))
+    xs = [x.numpy() for x in make_inputs(args.seed, T, "cpu")]
+    used = 1
+
+    def step():
+        nonlocal used
+        for l in range(nl):
+            _, used = layers[l](xs[l])
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps * (LAYERS / nl)
+    val = T / dt
+    sample = "%d of 8 layers per step, scaled to 8; AVX2 dots, OpenMP over rows grouped by expert" % nl
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x int2/int3 dot, f32 accumulate", "data": "synthetic",
+            "config": {"workload": workload_name(T), "tokens_per_step": T},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": used, "kind": "port", "sample": sample,
+                             "host_cores": cores},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=16, help="tokens per step per GPU (1, 4 or 16 in the sweep)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seed", type=int, default=20261125)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the extra batch sizes of the sweep")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--layers", type=int, default=8, help="layers in the stack (8 = the benchmark configuration; "
+                    "fewer only for profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    global LAYERS
+    LAYERS = args.layers
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from zeromoe_b200 import lib
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib.load()
+
+    T = args.tokens
+    e_lo, e_hi = rank * E // world, (rank + 1) * E // world
+    n_local = e_hi - e_lo
+    t_all = T * world
+    ctx = lib.Context(max(t_all, 16), D, F, E, K)
+    layers, weights = [], []
+    for l in range(LAYERS):
+        wg, wu, wd, wr = make_layer_weights(args.seed, l, dev, e_lo, e_hi)
+        weights.append((wg, wu, wd, wr))
+        layers.append(lib.Layer(ctx, D, F, n_local, K, TYPES, wg, wu, wd, router_w=wr if world == 1 else None))
+    xs = make_inputs(args.seed, T, dev, rank)
+    outs = [torch.empty((T, D), device=dev) for _ in range(LAYERS)]
+    stream = torch.cuda.current_stream()
+
+    graph = None
+    if world == 1:
+        def step_eager():
+            for l in range(LAYERS):
+                layers[l].forward(xs[l], outs[l])     # enqueues on torch's current stream
+        step = step_eager
+        if not args.no_graph:
+            # the library only enqueues kernels on the stream it is given, so a step can be
+            # captured once and replayed (the reference replays its MoE graphs the same way)
+            for _ in range(2):
+                step_eager()
+            torch.cuda.synchronize()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step_eager()
+                step = graph.replay
+            except Exception as exc:      # capture not possible: time eager launches, say so
+                graph = None
+                step = step_eager
+                sys.stderr.write("graph capture failed, timing eager launches: %r\n" % (exc,))
+    else:
+        from zeromoe_b200 import expert_parallel as ep
+        shard = ep.ExpertShard(ctx, rank, world, E, K, D, F, TYPES, weights, dev)
+
+        def step():
+            for l in range(LAYERS):
+                shard.forward(l, xs[l], outs[l])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(steps):
+            fn()
+        ev1.record(stream)
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    # kernels per step, counted by the library on an eager step (a graph replay launches the same nodes)
+    launches0 = lib.load().zmoe_kernel_launches()
+    if world == 1:
+        step_eager()
+    else:
+        step()
+    launches_per_step = lib.load().zmoe_kernel_launches() - launches0
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = launches_per_step * args.steps
+    ctx.check()
+    value = t_all / (ms_step * 1e-3)
+
+    # ---- end to end through the host-buffer entry --------------------------------------
+    e2e = None
+    if world == 1:
+        xh = [x.cpu().pin_memory() for x in xs]
+        oh = [torch.empty((T, D), dtype=torch.float32).pin_memory() for _ in range(LAYERS)]
+
+        def step_host():
+            for l in range(LAYERS):
+                layers[l].forward_host(xh[l], oh[l])
+        for _ in range(3):
+            step_host()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_host()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / args.steps
+        e2e = {"value": T / dt, "unit": UNIT, "h2d_bytes_per_step": LAYERS * T * D * 4,
+               "d2h_bytes_per_step": LAYERS * T * D * 4, "ms_per_step": dt * 1e3,
+               "api": "zmoe_moe_forward_host per layer (pinned host in, host out, stream sync per layer)"}
+        assert torch.equal(oh[0], outs[0].cpu()), "host entry and device entry disagree"
+
+    # ---- roofline of the dominant kernel (gate/up matmul + SwiGLU) ---------------------
+    roofline, layer_roofline = None, None
+    if world == 1 and rank == 0:
+        peaks, which = measured_peaks()
+        # distinct experts hit per layer decide the algorithmic bytes
+        nact = []
+        for l in range(LAYERS):
+            layers[l].route(xs[l], stream)
+            torch.cuda.synchronize()
+            nact.append(int((ctx.expert_freq(E) > 0).sum()))
+        gu_bytes = [n * 2 * F * RB_GU for n in nact]
+        dn_bytes = [n * D * RB_DN for n in nact]
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(LAYERS)]
+        reps, gu_ms = max(5, args.steps // 5), 0.0
+        for r in range(3 + reps):
+            for l in range(LAYERS):
+                layers[l].route(xs[l], stream)
+                layers[l].expert_ffn_timed(outs[l], evs[l][0], evs[l][1], stream)
+            torch.cuda.synchronize()
+            if r >= 3:
+                gu_ms += sum(a.elapsed_time(b) for a, b in evs)
+        gu_ms /= reps * LAYERS
+        ach = (sum(gu_bytes) / LAYERS) / (gu_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "mmid_kernel<Q2_K, dual> (gate/up matmul + SwiGLU)", "achieved": ach,
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_source": which,
+                    "avg_launch_ms": gu_ms, "bytes_per_launch": sum(gu_bytes) / LAYERS, "traffic": None,
+                    "distinct_experts_per_layer": nact}
+        step_bytes = sum(gu_bytes) + sum(dn_bytes) + LAYERS * E * D * 4
+        layer_roofline = {"algorithmic_bytes_per_step": step_bytes, "achieved": step_bytes / (ms_step * 1e-3) / 1e9,
+                          "unit": "GB/s", "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                          "frac_of_8TBs_nominal": step_bytes / (ms_step * 1e-3) / 8e12}
+
+    # ---- the other batch sizes of the sweep --------------------------------------------
+    sweep = {}
+    if world == 1 and not args.no_sweep:
+        for t2 in (1, 4, 16):
+            if t2 == T:
+                sweep[str(t2)] = {"tokens_per_s": value, "ms_per_step": ms_step}
+                continue
+            xs2 = make_inputs(args.seed, t2, dev, rank)
+            outs2 = [torch.empty((t2, D), device=dev) for _ in range(LAYERS)]
+
+            def step2():
+                for l in range(LAYERS):
+                    layers[l].forward(xs2[l], outs2[l])
+            for _ in range(args.warmup):
+                step2()
+            fn2 = step2
+            if graph is not None:
+                torch.cuda.synchronize()
+                g2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g2):
+                    step2()
+                fn2 = g2.replay
+                fn2()
+            ms2 = timed(fn2, args.steps)
+            sweep[str(t2)] = {"tokens_per_s": t2 / (ms2 * 1e-3), "ms_per_step": ms2}
+
+    # ---- CPU baseline on a bounded sample -----------------------------------------------
+    cpu = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        wg, wu, wd, wr = (w.cpu().numpy() for w in weights[0])
+        run = cpu_layer_runner(wg, wu, wd, wr)
+        x0 = xs[0].cpu().numpy()
+        ref_out, used = run(x0)
+        got = outs[0].cpu().numpy() if T == args.tokens else None
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 200):
+            run(x0)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps * LAYERS
+        layers[0].forward(xs[0], outs[0], stream)
+        torch.cuda.synchronize()
+        err = float(np.abs(outs[0].cpu().numpy() - ref_out).max() / np.linalg.norm(ref_out))
+        cpu = {"value": T / dt, "unit": UNIT, "cores": used, "kind": "port",
+               "sample": "layer 0 of 8 (router + expert FFN), %d repetitions, scaled to 8 layers" % reps,
+               "host_cores": os.cpu_count(), "gpu_vs_cpu_max_abs_err_rel_to_norm": err}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "int8 x int2/int3 dot, f32 accumulate", "data": "synthetic",
+                "config": {"workload": workload_name(T), "tokens_per_step_per_gpu": T, "layers": LAYERS,
+                           "parallelism": "ep%d" % world if world > 1 else "single",
+                           "l2": "inputs larger than L2: 7.0 GB of expert weights cycle every step",
+                           "launch": "cuda graph replay" if graph is not None else "eager"},
+                "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "roofline": roofline,
+                "layer_stack_roofline": layer_roofline, "sweep": sweep, "cpu_baseline": cpu}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,198 @@
+/*
+ * zmoe_b200.h -- C ABI of libzmoe_b200.so: the MoE expert hot path of
+ * ray-x/ZeroMoE (router top-k, token-to-expert grouping, quantised expert FFN,
+ * weighted combine) for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only.  All pointers named *_dev are device pointers
+ * on the current CUDA device; `stream` is a cudaStream_t passed as void*.
+ * Functions that return int return 0 on success and a negative ZMOE_ERR_* code
+ * otherwise; there is no CPU fallback anywhere in the library.
+ *
+ * Numerics: activations are quantised to Q8_K per 256 values and multiplied in
+ * integer arithmetic, as the reference's CPU path (ggml MUL_MAT_ID) does; the
+ * per-super-block int32 sums are exact, f32 assembly differs only in summation
+ * order.
+ */
+#ifndef ZMOE_B200_H
+#define ZMOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#else
+#include <stdbool.h>
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+#define ZMOE_OK 0
+#define ZMOE_ERR_ARG (-1)         /* null pointer, non-positive size, inconsistent shapes */
+#define ZMOE_ERR_TYPE (-2)        /* quantisation type without a kernel */
+#define ZMOE_ERR_SHAPE (-3)       /* row length not a multiple of 256 or out of range */
+#define ZMOE_ERR_ALIGN (-4)       /* weight pointer / stride not 16-byte aligned */
+#define ZMOE_ERR_CUDA (-5)        /* a CUDA runtime call failed */
+#define ZMOE_ERR_CAPACITY (-6)    /* more tokens than the context was created for */
+#define ZMOE_ERR_DEVICE_WAIT (-7) /* a bounded device-side wait expired */
+#define ZMOE_ERR_STATE (-8)       /* wrong call order */
+
+/* GGUF quantisation type ids (reference models/base/gguf_loader.hpp:28-51) */
+#define ZMOE_TYPE_Q2_K 10
+#define ZMOE_TYPE_Q3_K 11
+#define ZMOE_TYPE_Q4_K 12
+#define ZMOE_TYPE_IQ2_XXS 16
+
+/* router gating (reference models/base/gguf_loader.hpp:177-181) */
+#define ZMOE_GATING_SOFTMAX 0
+#define ZMOE_GATING_SIGMOID 1
+#define ZMOE_GATING_SQRT_SOFTPLUS 2
+
+/* =========================================================================
+ * 1. Kernel-launch ABI -- the symbols the reference's CudaKernelDispatcher and
+ *    cuda_manager link against.  y[S,O] = x[S,I] . W[O,I]^T, W packed rows of
+ *    quantised super-blocks, device pointers, asynchronous, void return
+ *    (errors surface through cudaGetLastError / zmoe_last_status()).
+ *    They use the library's per-device scratch for the quantised activations;
+ *    call zmoe_reserve() first when launching under stream capture.
+ * ========================================================================= */
+
+/* replaces reference kernels/quant/kquant_matmul.cu:576-590 */
+void launch_q2_K_matmul(float *y, const float *x, const void *w, int S, int I, int O);
+void launch_q2_K_matmul_stream(float *y, const float *x, const void *w, int S, int I, int O, void *stream);
+/* replaces reference kernels/quant/kquant_matmul.cu:591-601 */
+void launch_q3_K_matmul(float *y, const float *x, const void *w, int S, int I, int O);
+void launch_q3_K_matmul_stream(float *y, const float *x, const void *w, int S, int I, int O, void *stream);
+/* replaces reference kernels/quant/kquant_matmul.cu:602-607 */
+void launch_q4_K_matmul(float *y, const float *x, const void *w, int S, int I, int O);
+/* replaces reference kernels/quant/iq2_matmul.cu:180-183 */
+void launch_iq2_xxs_matmul(float *y, const float *x, const void *w, int S, int I, int O);
+
+/* replaces reference kernels/math/expert_activation.cu:61-70 */
+void launch_expert_swiglu(float *prod, const float *gate, const float *up, int n, float clamp, int fused,
+                          int *d_bad, void *stream);
+/* replaces reference kernels/math/expert_accum.cu:39-46 */
+void launch_expert_scatter_accum(const float *src, const int *tok, const float *w, float *dst, int n, int D,
+                                 int S, void *stream);
+/* replaces reference kernels/math/expert_accum.cu:52-60 */
+void launch_expert_scatter_add(const float *src, const int *tok, float *dst, int n, int D, int S, void *stream);
+/* replaces reference kernels/models/glm5next_router.cu:95-105 */
+void launch_glm5next_router_topk(float *logits, const float *bias, int32_t *ids, float *weights, int S,
+                                 int n_experts, int topk, int gating_func, int normalize, float weight_scale,
+                                 void *stream);
+
+/* grow the per-device scratch of the entry points above to hold `rows`
+ * activation rows of `I` elements (allocates; not capturable) */
+int zmoe_reserve(int rows, int I);
+/* status of the most recent kernel-launch-ABI call on this thread */
+int zmoe_last_status(void);
+
+/* =========================================================================
+ * 2. ggml backend op hook -- replaces the hook the reference registers with
+ *    ggml-cuda for GGML_OP_MUL_MAT / GGML_OP_MUL_MAT_ID nodes
+ *    (reference kernels/quant/kquant_matmul.cu:702-765,
+ *    patches/ggml/0010-native-f32-quant-graph-hook.patch).  ggml is not part of
+ *    this library, so the tensors arrive as a plain mirror of the ggml_tensor
+ *    fields the hook reads; a trampoline from real ggml_tensor is a few lines.
+ * ========================================================================= */
+typedef struct zmoe_tensor {
+    int type;       /* ggml type id: 0 = F32, 26 = I32, or a ZMOE_TYPE_* */
+    int64_t ne[4];  /* elements per dimension */
+    size_t nb[4];   /* strides in bytes */
+    void *data;     /* device pointer */
+} zmoe_tensor;
+
+/* Same contract as the reference hook: returns false when the node is not
+ * handled; execute=false is a side-effect-free support query; with
+ * execute=true the work is enqueued on `stream`.
+ *   w->ne = [I, O, E, 1], rows packed (w->nb[1] == row bytes), w->nb[2] free;
+ *   x->ne = [I, 1|K, T]; ids->ne = [K, T] (I32) or ids == NULL for MUL_MAT;
+ *   y->ne = [O, K, T].  ids < 0 -> zero row, ids >= E -> NaN row. */
+bool zmoe_f32_quant_hook(const zmoe_tensor *w, const zmoe_tensor *x, const zmoe_tensor *ids, zmoe_tensor *y,
+                         void *stream, bool execute);
+/* replaces reference kernels/quant/kquant_matmul.cu:757-765; returns false
+ * because no ggml-cuda is linked into this library to register with */
+bool zeromoe_install_f32_quant_graph_hook(void);
+uint64_t zeromoe_f32_quant_graph_launches(void);
+
+/* =========================================================================
+ * 3. Layer-level entry -- replaces, for HBM-resident weights,
+ *    MoeRouterService::route (reference core/moe_router_service.cpp:430),
+ *    BatchedDispatchPipeline::run (reference core/batched_dispatch_pipeline.hpp:5-14)
+ *    and expert_ffn_gpu_issue / finish_stage1 / finish_stage2
+ *    (reference core/gpu_expert_executor.hpp:42-58).
+ * ========================================================================= */
+typedef struct zmoe_ctx zmoe_ctx;     /* per-device scratch, one per decode thread */
+typedef struct zmoe_layer zmoe_layer; /* borrowed weights of one MoE layer */
+
+typedef struct zmoe_weight {
+    const void *data_dev;  /* expert 0, row 0 */
+    size_t expert_stride;  /* bytes between experts (>= rows * row bytes) */
+    size_t bytes;          /* bytes addressable from data_dev; 0 = n_experts * expert_stride */
+    int type;              /* ZMOE_TYPE_* */
+} zmoe_weight;
+
+typedef struct zmoe_layer_desc {
+    int d_model, d_ff, n_experts, topk;
+    zmoe_weight gate, up, down;  /* gate/up: [E][d_ff rows of d_model]; down: [E][d_model rows of d_ff] */
+    const float *router_w_dev;   /* [n_experts, d_model] f32, may be NULL when routes are always supplied */
+    const float *router_bias_dev;/* [n_experts] selection bias or NULL */
+    int gating;                  /* ZMOE_GATING_* */
+    int weights_norm;            /* expert_weights_norm */
+    float weights_scale;         /* expert_weights_scale; 0 or 1 = none */
+    int n_groups, n_groups_used; /* group-limited routing; n_groups <= 1 disables */
+    float swiglu_clamp;          /* <= 0: none */
+    int swiglu_clamp_fused;      /* clamp gate/up before the activation instead of the product */
+} zmoe_layer_desc;
+
+int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_experts, int max_topk, zmoe_ctx **out);
+void zmoe_ctx_destroy(zmoe_ctx *ctx);
+int zmoe_layer_create(zmoe_ctx *ctx, const zmoe_layer_desc *desc, zmoe_layer **out);
+void zmoe_layer_destroy(zmoe_layer *layer);
+
+/* router + grouping: fills the context's route table (ids, weights, expert
+ * histogram, CSR) for T tokens of x_dev [T, d_model]. */
+int zmoe_route(zmoe_layer *layer, const float *x_dev, int T, void *stream);
+/* supply routes computed elsewhere (ids [T, topk] i32, weights [T, topk] f32, device);
+ * negative ids are inactive routes */
+int zmoe_set_routes(zmoe_layer *layer, const float *x_dev, const int32_t *ids_dev, const float *weights_dev, int T,
+                    void *stream);
+/* expert FFN + combine over the current routes: out_dev [T, d_model] is
+ * overwritten (accumulate = 0) or added to (accumulate = 1) */
+int zmoe_expert_ffn(zmoe_layer *layer, float *out_dev, int T, int accumulate, void *stream);
+/* zmoe_expert_ffn that also records two caller-owned cudaEvent_t (passed as void*) on
+ * `stream`, one before and one after the gate/up matmul, for per-kernel timing */
+int zmoe_expert_ffn_events(zmoe_layer *layer, float *out_dev, int T, int accumulate, void *stream,
+                           void *ev_before_gate_up, void *ev_after_gate_up);
+/* zmoe_route followed by zmoe_expert_ffn */
+int zmoe_moe_forward(zmoe_layer *layer, const float *x_dev, float *out_dev, int T, void *stream);
+/* the same with host buffers: copies x in, runs the layer, copies out back, synchronises */
+int zmoe_moe_forward_host(zmoe_layer *layer, const float *x_host, float *out_host, int T);
+
+/* copies of the current route table / intermediates to host (synchronise the stream first) */
+int zmoe_get_routes(zmoe_ctx *ctx, int T, int topk, int32_t *ids_host, float *weights_host);
+int zmoe_get_expert_freq(zmoe_ctx *ctx, int n_experts, int32_t *freq_host);
+int zmoe_get_probs(zmoe_ctx *ctx, int T, int n_experts, float *probs_host);
+int zmoe_get_act(zmoe_ctx *ctx, int n_pairs, int d_ff, float *act_host);
+/* reads and clears the device error flag: 0, or ZMOE_ERR_DEVICE_WAIT */
+int zmoe_ctx_check(zmoe_ctx *ctx);
+/* number of kernels this library has launched since load (all entry points) */
+uint64_t zmoe_kernel_launches(void);
+
+/* =========================================================================
+ * 4. Parity hooks -- expose the integer stages so tests can compare them
+ *    bit-for-bit with the CPU path.
+ * ========================================================================= */
+/* x_dev [rows, I] f32 -> blocks_dev: rows * I/256 ggml Q8_K blocks of 292 bytes
+ * (layout: reference backends/cpu/kernels_cpu.cpp:22-26).  Internally the rows are
+ * quantised into the packed layout used against weights of `for_type` and regrouped;
+ * the blocks are the same for every type. */
+int zmoe_quantize_q8_K(const float *x_dev, void *blocks_dev, int rows, int I, int for_type, void *stream);
+/* per-super-block integer sums of weight row r against activation row r:
+ * isum = sum scale*(q.q8), msum = sum min*bsum; outputs [rows, I/256] i32 */
+int zmoe_block_isums(int type, const void *w_dev, const float *x_dev, int32_t *isum_dev, int32_t *msum_dev, int rows,
+                     int I, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZMOE_B200_H */

@@ -457,6 +457,7 @@ void zo_swiglu(float *prod, const float *gate, const float *up, int n, float cla
 /* router                                                               */
 /* ------------------------------------------------------------------ */
 void zo_router_logits(float *logits, const float *x, const float *wr, int T, int D, int E) {
+#pragma omp parallel for collapse(2) schedule(static)
     for (int t = 0; t < T; ++t)
         for (int e = 0; e < E; ++e) {
             double a = 0.0;

@@ -1,0 +1,436 @@
+"""GPU parity tests: every stage of the CUDA path, called through the C ABI,
+against the CPU oracle on the same seeded inputs.
+
+Integer stages (Q8_K bytes, per-super-block int32 sums, expert ids, grouping)
+must match bit for bit; f32 outputs within 1e-3 max-abs relative to the norm
+of the reference output (helpers.REL_TO_NORM).  Shapes and recipes follow the
+reference's own tests: tests/native/tests_basic_cuda.cpp:301-320,367,414
+(matmul shapes), tests/test_phase_alias_numerics.cpp:104-107 (exact inputs),
+tests/test_qwen_moe_router_ggml.cpp:22-188 (router literals),
+tests/test_option_b_compact_ggml.cpp:21-145 (negative ids),
+tests/test_dsv41_cache_graph.cpp:60-185 (strided slabs, untouched weights),
+tests/native/tests_expert_cache.cpp:772-841 (device accumulate).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from helpers import REL_TO_NORM, TYPES, rel_to_norm, routed_inputs, to_dev
+from zeromoe_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _sync():
+    import torch
+    torch.cuda.synchronize()
+
+
+# ---------------------------------------------------------------------------
+# activation quantisation
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("for_type", [synth.Q2_K, synth.Q4_K])     # the two packed-row layouts
+def test_q8k_bytes_bit_exact(zlib, oracle, dev, for_type):
+    import torch
+    rng = synth.rng_for(11, 0)
+    rows, I = 7, 2048
+    x = synth.activations(rows, I, rng)
+    x[1, 256:512] = 0.0                       # an all-zero super-block
+    x[2, 0:256] *= 1e-20                      # tiny magnitudes
+    x[3, 0:256] *= 1e20                       # huge magnitudes
+    x[4, 10] = 9.0
+    x[4, 200] = -9.0                          # |max| tie with opposite signs: first wins
+    x[5, 256:512] = np.round(x[5, 256:512] * 4) / 4 + 0.5   # many exact .5 products
+    x[6, :] = synth.exact_activations(1, I, rng)[0]
+    xd = to_dev(x, dev)
+    out = torch.zeros(rows * (I // 256) * 292, dtype=torch.uint8, device=dev)
+    zlib.check(zlib.load().zmoe_quantize_q8_K(zlib.ptr(xd), zlib.ptr(out), rows, I, for_type, None),
+               "zmoe_quantize_q8_K")
+    _sync()
+    got = out.cpu().numpy().reshape(rows, -1)
+    ref = oracle.quantize_q8_K(x)
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_block_int32_sums_bit_exact(zlib, oracle, dev, qtype):
+    import torch
+    rng = synth.rng_for(12, qtype)
+    rows, I = 24, 1536
+    nb = I // 256
+    w = synth.random_blocks(qtype, rows * nb, rng).reshape(rows, -1)
+    x = synth.activations(rows, I, rng) * rng.uniform(0.1, 4.0, size=(rows, 1)).astype(np.float32)
+    wd, xd = to_dev(w, dev), to_dev(x, dev)
+    isum = torch.zeros((rows, nb), dtype=torch.int32, device=dev)
+    msum = torch.zeros((rows, nb), dtype=torch.int32, device=dev)
+    zlib.check(zlib.load().zmoe_block_isums(qtype, zlib.ptr(wd), zlib.ptr(xd), zlib.ptr(isum), zlib.ptr(msum),
+                                            rows, I, None), "zmoe_block_isums")
+    _sync()
+    q8 = oracle.quantize_q8_K(x)
+    for r in range(rows):
+        ri, rm = oracle.block_isums(qtype, w[r], q8[r])
+        assert np.array_equal(isum[r].cpu().numpy(), ri), (qtype, r)
+        assert np.array_equal(msum[r].cpu().numpy(), rm), (qtype, r)
+
+
+# ---------------------------------------------------------------------------
+# launch_*_matmul (reference kernel-launch ABI)
+# ---------------------------------------------------------------------------
+MATMUL_SHAPES = [(512, 8, 3), (4096, 4, 2), (2048, 40, 1), (1536, 64, 5), (768, 12, 9), (7168, 16, 2), (256, 3, 1)]
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+@pytest.mark.parametrize("shape", MATMUL_SHAPES)
+def test_dense_matmul_vs_oracle(zlib, oracle, dev, qtype, shape):
+    I, O, S = shape
+    rng = synth.rng_for(13, qtype, I, O)
+    w = synth.expert_weights(qtype, 1, O, I, rng)[0]
+    x = synth.activations(S, I, rng)
+    y = zlib.dense_matmul(qtype, to_dev(x, dev), to_dev(w, dev), O)
+    _sync()
+    ref = oracle.matmul(qtype, x, w, S, I, O)
+    assert rel_to_norm(y.cpu().numpy(), ref) < REL_TO_NORM
+
+
+@pytest.mark.parametrize("qtype", TYPES)
+def test_dense_matmul_exact_inputs_vs_f64(zlib, oracle, dev, qtype):
+    """with activations that Q8_K represents exactly the result must agree with a
+    float64 dequantise-and-dot to 1e-4 relative L2 (the reference's EXACT_INPUTS check)"""
+    I, O, S = 4096, 48, 2
+    rng = synth.rng_for(14, qtype)
+    w = synth.expert_weights(qtype, 1, O, I, rng)[0]
+    x = synth.exact_activations(S, I, rng)
+    y = zlib.dense_matmul(qtype, to_dev(x, dev), to_dev(w, dev), O).cpu().numpy()
+    deq = oracle.dequantize(qtype, w, I).astype(np.float64)
+    ref = x.astype(np.float64) @ deq.T
+    assert np.linalg.norm(y - ref) / np.linalg.norm(ref) < 1e-4
+
+
+def test_dense_matmul_rejects_bad_shapes(zlib, dev):
+    import torch
+    x = torch.zeros((1, 300), device=dev)
+    w = torch.zeros(1024, dtype=torch.uint8, device=dev)
+    y = torch.zeros((1, 4), device=dev)
+    L = zlib.load()
+    L.launch_q4_K_matmul(zlib.ptr(y), zlib.ptr(x), zlib.ptr(w), 1, 300, 4)
+    assert L.zmoe_last_status() == -3
+    L.launch_q4_K_matmul(None, zlib.ptr(x), zlib.ptr(w), 1, 256, 4)
+    assert L.zmoe_last_status() == -1
+
+
+# ---------------------------------------------------------------------------
+# element-wise kernels of the reference ABI
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("clamp,fused", [(0.0, 0), (2.5, 0), (2.5, 1), (0.0, 1)])
+def test_expert_swiglu(zlib, oracle, dev, clamp, fused):
+    import torch
+    rng = synth.rng_for(15, int(clamp * 10), fused)
+    n = 5000
+    g = (rng.standard_normal(n) * 4).astype(np.float32)
+    u = (rng.standard_normal(n) * 2).astype(np.float32)
+    g[7] = np.nan
+    u[9] = np.inf
+    gd, ud = to_dev(g, dev), to_dev(u, dev)
+    out = torch.zeros(n, device=dev)
+    bad = torch.zeros(2, dtype=torch.int32, device=dev)
+    zlib.load().launch_expert_swiglu(zlib.ptr(out), zlib.ptr(gd), zlib.ptr(ud), n, clamp, fused, zlib.ptr(bad), None)
+    _sync()
+    ref = oracle.swiglu(g, u, clamp, fused)
+    got = out.cpu().numpy()
+    ok = np.isfinite(ref)
+    assert np.allclose(got[ok], ref[ok], rtol=2e-6, atol=1e-7)
+    assert bad.cpu().tolist() == [1, 1]
+
+
+def test_scatter_accum(zlib, dev):
+    import torch
+    rng = np.random.default_rng(777)
+    S, D, n = 9, 640, 6
+    src = rng.standard_normal((n, D)).astype(np.float32)
+    tok = np.array([3, 0, 8, 5, 3, 99], dtype=np.int32)   # repeated token, one out of range
+    w = rng.standard_normal(n).astype(np.float32)
+    dst = torch.zeros((S, D), device=dev)
+    L = zlib.load()
+    # rows of one call must target distinct tokens: issue the repeat as a second call
+    for sel in ([0, 1, 2, 3, 5], [4]):
+        s, t, ww = to_dev(src[sel], dev), to_dev(tok[sel], dev), to_dev(w[sel], dev)
+        L.launch_expert_scatter_accum(zlib.ptr(s), zlib.ptr(t), zlib.ptr(ww), zlib.ptr(dst), len(sel), D, S, None)
+    _sync()
+    ref = np.zeros((S, D), dtype=np.float32)
+    for i in range(n):
+        if 0 <= tok[i] < S:
+            ref[tok[i]] += w[i] * src[i]
+    got = dst.cpu().numpy()
+    assert np.allclose(got, ref, rtol=1e-6, atol=1e-6)
+    assert np.all(got[1] == 0.0)   # an untouched row stays exactly zero
+
+
+# ---------------------------------------------------------------------------
+# router
+# ---------------------------------------------------------------------------
+def test_router_reference_literals(zlib, dev):
+    """fixed 3x4 router, two tokens, softmax, top-2, normalise, scale 1.5"""
+    import torch
+    router = np.array([[1, 0, 0], [0, 1, 0], [0, 0, 1], [.5, .5, .5]], dtype=np.float32)
+    hidden = np.array([[0.1, 2.0, 1.0], [3.0, 0.5, -1.0]], dtype=np.float32)
+    logits = hidden @ router.T
+    ld = to_dev(logits, dev)
+    ids = torch.zeros((2, 2), dtype=torch.int32, device=dev)
+    w = torch.zeros((2, 2), dtype=torch.float32, device=dev)
+    zlib.load().launch_glm5next_router_topk(zlib.ptr(ld), None, zlib.ptr(ids), zlib.ptr(w), 2, 4, 2, 0, 1, 1.5, None)
+    _sync()
+    ex = np.exp(logits - logits.max(1, keepdims=True))
+    probs = ex / ex.sum(1, keepdims=True)
+    order = np.argsort(-probs, axis=1)[:, :2]
+    sel = np.take_along_axis(probs, order, 1)
+    assert np.array_equal(ids.cpu().numpy(), order.astype(np.int32))
+    assert np.allclose(w.cpu().numpy(), 1.5 * sel / sel.sum(1, keepdims=True), atol=1e-5)
+    assert np.allclose(ld.cpu().numpy(), probs, atol=1e-5)   # logits are overwritten with probabilities
+
+
+ROUTER_CASES = [
+    dict(E=128, K=8, gating=0, normalize=1, scale=0.0, groups=(0, 0), bias=False),
+    dict(E=128, K=8, gating=1, normalize=1, scale=2.5, groups=(0, 0), bias=True),
+    dict(E=256, K=8, gating=1, normalize=1, scale=2.5, groups=(8, 4), bias=True),
+    dict(E=64, K=6, gating=2, normalize=0, scale=1.0, groups=(0, 0), bias=False),
+    dict(E=11, K=4, gating=0, normalize=1, scale=0.0, groups=(0, 0), bias=False),
+]
+
+
+@pytest.mark.parametrize("case", ROUTER_CASES)
+@pytest.mark.parametrize("T", [1, 16, 37])
+def test_layer_router_vs_oracle(zlib, oracle, dev, case, T):
+    import torch
+    E, K, D, F = case["E"], case["K"], 512, 256
+    rng = synth.rng_for(16, E, K, T)
+    bias = (rng.standard_normal(E) * 0.05).astype(np.float32) if case["bias"] else None
+    wr, x, probs, ids_ref, w_ref = routed_inputs(oracle, 16 + E + T, T, D, E, K, gating=case["gating"],
+                                                 normalize=case["normalize"], weight_scale=case["scale"], bias=bias,
+                                                 n_groups=case["groups"][0], n_groups_used=case["groups"][1])
+    w = synth.expert_weights(synth.Q4_K, E, F, D, rng)
+    wdn = synth.expert_weights(synth.Q4_K, E, D, F, rng)
+    ctx = zlib.Context(64, D, F, E, K)
+    wd, wdd = to_dev(w, dev), to_dev(wdn, dev)
+    layer = zlib.Layer(ctx, D, F, E, K, (synth.Q4_K,) * 3, wd, wd, wdd, router_w=to_dev(wr, dev),
+                       router_bias=None if bias is None else to_dev(bias, dev), gating=case["gating"],
+                       weights_norm=case["normalize"], weights_scale=case["scale"], n_groups=case["groups"][0],
+                       n_groups_used=case["groups"][1])
+    layer.route(to_dev(x, dev))
+    _sync()
+    ctx.check()
+    ids, wts = ctx.routes(T, K)
+    assert np.array_equal(ids, ids_ref)
+    assert np.allclose(wts, w_ref, atol=1e-5)
+    assert np.allclose(ctx.probs(T, E), probs, atol=1e-5)
+    offs, _ = oracle.group_by_expert(ids_ref, E)
+    assert np.array_equal(ctx.expert_freq(E), np.diff(offs))
+
+
+# ---------------------------------------------------------------------------
+# the whole layer
+# ---------------------------------------------------------------------------
+LAYER_CASES = [
+    # D, F, E, K, types (gate, up, down), T
+    (2048, 768, 128, 8, (synth.Q4_K, synth.Q4_K, synth.Q4_K), 1),       # benchmark configuration 1, decode
+    (2048, 768, 128, 8, (synth.Q4_K, synth.Q4_K, synth.Q4_K), 64),      # configuration 1, 64 tokens
+    (4096, 1536, 128, 8, (synth.Q2_K, synth.Q2_K, synth.Q3_K), 1),      # configuration 2
+    (4096, 1536, 128, 8, (synth.Q2_K, synth.Q2_K, synth.Q3_K), 16),
+    (4096, 1536, 32, 8, (synth.IQ2_XXS, synth.IQ2_XXS, synth.IQ2_XXS), 5),   # configuration 3's types
+    (1024, 512, 16, 4, (synth.Q2_K, synth.Q4_K, synth.Q3_K), 7),        # gate and up of different types
+    (512, 256, 8, 8, (synth.Q3_K, synth.Q3_K, synth.Q2_K), 3),          # every expert used by every token
+]
+
+
+@pytest.mark.parametrize("case", LAYER_CASES)
+def test_moe_layer_vs_oracle(zlib, oracle, dev, case):
+    import torch
+    D, F, E, K, types, T = case
+    rng = synth.rng_for(17, D, F, E, T)
+    wg = synth.expert_weights(types[0], E, F, D, rng)
+    wu = synth.expert_weights(types[1], E, F, D, rng)
+    wd = synth.expert_weights(types[2], E, D, F, rng)
+    wr, x, probs, ids_ref, w_ref = routed_inputs(oracle, 17 + D + T, T, D, E, K)
+    ctx = zlib.Context(64, D, F, E, K)
+    tg, tu, td = to_dev(wg, dev), to_dev(wu, dev), to_dev(wd, dev)
+    canary = [t.clone() for t in (tg, tu, td)]
+    layer = zlib.Layer(ctx, D, F, E, K, types, tg, tu, td, router_w=to_dev(wr, dev))
+    out = torch.full((T, D), float("nan"), device=dev)
+    layer.forward(to_dev(x, dev), out)
+    _sync()
+    ctx.check()
+    ids, wts = ctx.routes(T, K)
+    assert np.array_equal(ids, ids_ref)
+    Lr = oracle.make_layer(D, F, E, K, types, wg, wu, wd)
+    ref, act_ref = oracle.moe_ffn(Lr, x, ids_ref, w_ref, want_act=True)
+    act = ctx.act(T * K, F).reshape(T, K, F)
+    assert rel_to_norm(act, act_ref) < REL_TO_NORM
+    assert rel_to_norm(out.cpu().numpy(), ref) < REL_TO_NORM
+    # weights are borrowed and must stay bit-identical
+    for t, c in zip((tg, tu, td), canary):
+        assert torch.equal(t, c)
+    # the same call again gives the same bytes (fixed reduction order)
+    out2 = torch.empty_like(out)
+    layer.forward(to_dev(x, dev), out2)
+    _sync()
+    assert torch.equal(out, out2)
+
+
+def test_moe_layer_supplied_routes_with_inactive_ids(zlib, oracle, dev):
+    """negative ids are inactive routes: they contribute a zero row"""
+    import torch
+    D, F, E, K, T = 1024, 512, 12, 10, 6
+    types = (synth.Q2_K, synth.Q2_K, synth.Q3_K)
+    rng = synth.rng_for(18, 0)
+    wg = synth.expert_weights(types[0], E, F, D, rng)
+    wu = synth.expert_weights(types[1], E, F, D, rng)
+    wd = synth.expert_weights(types[2], E, D, F, rng)
+    x = synth.activations(T, D, rng)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(T)]).astype(np.int32)
+    ids[0, 3] = -1
+    ids[2, :] = -1          # a token with no active route at all
+    ids[5, 9] = -1
+    wts = rng.uniform(0.05, 0.3, size=(T, K)).astype(np.float32)
+    ctx = zlib.Context(8, D, F, E, K)
+    layer = zlib.Layer(ctx, D, F, E, K, types, to_dev(wg, dev), to_dev(wu, dev), to_dev(wd, dev))
+    xd = to_dev(x, dev)
+    layer.set_routes(xd, to_dev(ids, dev), to_dev(wts, dev))
+    out = torch.full((T, D), float("nan"), device=dev)
+    layer.expert_ffn(out)
+    _sync()
+    ctx.check()
+    Lr = oracle.make_layer(D, F, E, K, types, wg, wu, wd)
+    ref = oracle.moe_ffn(Lr, x, ids, wts)
+    got = out.cpu().numpy()
+    assert rel_to_norm(got, ref) < REL_TO_NORM
+    assert np.all(got[2] == 0.0)
+    # accumulate = 1 adds to what is there
+    base = torch.ones((T, D), device=dev)
+    layer.expert_ffn(base, accumulate=1)
+    _sync()
+    assert rel_to_norm(base.cpu().numpy(), ref + 1.0) < REL_TO_NORM
+
+
+def test_moe_forward_host_buffers(zlib, oracle, dev):
+    import torch
+    D, F, E, K, T = 1024, 512, 16, 4, 4
+    types = (synth.Q4_K,) * 3
+    rng = synth.rng_for(19, 0)
+    wg = synth.expert_weights(types[0], E, F, D, rng)
+    wu = synth.expert_weights(types[1], E, F, D, rng)
+    wd = synth.expert_weights(types[2], E, D, F, rng)
+    wr, x, probs, ids_ref, w_ref = routed_inputs(oracle, 19, T, D, E, K)
+    ctx = zlib.Context(8, D, F, E, K)
+    layer = zlib.Layer(ctx, D, F, E, K, types, to_dev(wg, dev), to_dev(wu, dev), to_dev(wd, dev),
+                       router_w=to_dev(wr, dev))
+    xh = torch.from_numpy(x).pin_memory()
+    oh = torch.empty((T, D), dtype=torch.float32).pin_memory()
+    layer.forward_host(xh, oh)
+    ref = oracle.moe_ffn(oracle.make_layer(D, F, E, K, types, wg, wu, wd), x, ids_ref, w_ref)
+    assert rel_to_norm(oh.numpy(), ref) < REL_TO_NORM
+
+
+def test_capacity_and_state_errors(zlib, dev):
+    import torch
+    D, F, E, K = 512, 256, 8, 2
+    rng = synth.rng_for(20, 0)
+    w = to_dev(synth.expert_weights(synth.Q4_K, E, F, D, rng), dev)
+    wd = to_dev(synth.expert_weights(synth.Q4_K, E, D, F, rng), dev)
+    ctx = zlib.Context(4, D, F, E, K)
+    layer = zlib.Layer(ctx, D, F, E, K, (synth.Q4_K,) * 3, w, w, wd,
+                       router_w=torch.zeros((E, D), device=dev))
+    x = torch.zeros((5, D), device=dev)
+    with pytest.raises(zlib.ZmoeError) as e:
+        layer.route(x)
+    assert e.value.code == -6
+    out = torch.zeros((2, D), device=dev)
+    with pytest.raises(zlib.ZmoeError) as e:
+        layer.expert_ffn(out)           # no routing for two tokens yet
+    assert e.value.code == -8
+    with pytest.raises(zlib.ZmoeError) as e:
+        zlib.Layer(ctx, D, F, E, K, (synth.Q4_K, synth.Q4_K, 7), w, w, wd)   # a type without a kernel
+    assert e.value.code == -2
+
+
+# ---------------------------------------------------------------------------
+# MUL_MAT_ID through the backend-op hook
+# ---------------------------------------------------------------------------
+def _hook_tensors(zlib, qtype, slab, off, I, O, E, stride, xd, K, T, x_per_route, ids_d, y):
+    import torch
+    rb = I // 256 * zlib.BLOCK_BYTES.get(qtype, 34)
+    w = zlib.Tensor()
+    w.type = qtype
+    w.ne[:] = [I, O, E, 1]
+    w.nb[:] = [0, rb, stride, stride * E]
+    w.data = slab.data_ptr() + off
+    x = zlib.Tensor()
+    x.type = zlib.GGML_F32
+    xr = K if x_per_route else 1
+    x.ne[:] = [I, xr, T, 1]
+    x.nb[:] = [4, 4 * I, 4 * I * xr, 4 * I * xr * T]
+    x.data = xd.data_ptr()
+    ids = zlib.Tensor()
+    ids.type = zlib.GGML_I32
+    ids.ne[:] = [K, T, 1, 1]
+    ids.nb[:] = [4, 4 * K, 4 * K * T, 4 * K * T]
+    ids.data = ids_d.data_ptr()
+    yt = zlib.Tensor()
+    yt.type = zlib.GGML_F32
+    yt.ne[:] = [O, K, T, 1]
+    yt.nb[:] = [4, 4 * O, 4 * O * K, 4 * O * K * T]
+    yt.data = y.data_ptr()
+    return w, x, ids, yt
+
+
+@pytest.mark.parametrize("T", [1, 19])
+def test_hook_mul_mat_id_strided_slab(zlib, oracle, dev, T):
+    """gate|up|down slabs per expert viewed in place: each projection equals the planar
+    layout bit for bit, ids -1 give zero rows, ids >= E give NaN rows, weights untouched"""
+    import torch
+    D, F, E, K = 256, 256, 9, 6
+    qg, qd = synth.Q2_K, synth.Q3_K
+    rng = synth.rng_for(21, T)
+    wg = synth.expert_weights(qg, E, F, D, rng)
+    wu = synth.expert_weights(qg, E, F, D, rng)
+    wd = synth.expert_weights(qd, E, D, F, rng)
+    gb, db = wg[0].size, wd[0].size
+    stride = (2 * gb + db + 15) // 16 * 16
+    slab = np.zeros((E, stride), dtype=np.uint8)
+    slab[:, :gb] = wg.reshape(E, -1)
+    slab[:, gb:2 * gb] = wu.reshape(E, -1)
+    slab[:, 2 * gb:2 * gb + db] = wd.reshape(E, -1)
+    slab_d = to_dev(slab, dev)
+    keep = slab_d.clone()
+    x = synth.activations(T, D, rng)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(T)]).astype(np.int32)
+    ids[0, 1] = -1
+    if T > 1:
+        ids[3, 2] = E + 5
+    xd, ids_d = to_dev(x, dev), to_dev(ids, dev)
+    L = zlib.load()
+    y_slab = torch.full((T, K, F), 7.0, device=dev)
+    args = _hook_tensors(zlib, qg, slab_d, gb, D, F, E, stride, xd, K, T, False, ids_d, y_slab)   # the "up" plane
+    assert L.zmoe_f32_quant_hook(*[C.byref(a) for a in args], None, False)     # support query
+    assert torch.all(y_slab == 7.0)                                             # ... has no side effect
+    assert L.zmoe_f32_quant_hook(*[C.byref(a) for a in args], None, True)
+    planar = to_dev(wu, dev)
+    y_planar = torch.full((T, K, F), 7.0, device=dev)
+    args2 = _hook_tensors(zlib, qg, planar, 0, D, F, E, wu[0].size, xd, K, T, False, ids_d, y_planar)
+    assert L.zmoe_f32_quant_hook(*[C.byref(a) for a in args2], None, True)
+    _sync()
+    a, b = y_slab.cpu().numpy(), y_planar.cpu().numpy()
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    ref = oracle.mul_mat_id(qg, x, wu, wu[0].size, ids, T, K, E, D, F, 0)
+    valid = (ids >= 0) & (ids < E)
+    assert rel_to_norm(a[valid], ref[valid]) < REL_TO_NORM
+    assert np.all(a[0, 1] == 0.0)
+    if T > 1:
+        assert np.all(np.isnan(a[3, 2]))
+    # each valid pair equals the stand-alone dense launch on that expert, bit for bit
+    t, k = (T - 1, K - 1)
+    dense = zlib.dense_matmul(qg, xd[t:t + 1].contiguous(), to_dev(wu[ids[t, k]], dev), F).cpu().numpy()
+    assert np.array_equal(dense[0].view(np.uint32), a[t, k].view(np.uint32))
+    assert torch.equal(slab_d, keep)
+    # unsupported nodes are declined, not mis-computed
+    bad = _hook_tensors(zlib, 8, slab_d, 0, D, F, E, stride, xd, K, T, False, ids_d, y_slab)    # Q8_0
+    assert not L.zmoe_f32_quant_hook(*[C.byref(a) for a in bad], None, False)

@@ -1,0 +1,388 @@
+// kernels_misc.cu -- the small kernels around the expert matmuls: router with
+// fused activation quantisation and planning, stand-alone planners, the Q8_K
+// row quantiser, the weighted combine, and the reference-ABI SwiGLU /
+// scatter-accumulate / router-top-k kernels.
+#include "q8k.cuh"
+#include "router.cuh"
+#include "zmoe_internal.h"
+
+namespace zmoe {
+
+// ------------------------------------------------------------------------
+// decode-shaped router.  CTA (e, g) computes the logit of expert e for the
+// ROUTER_TPB tokens of group g, with the expert's router row held in registers,
+// and quantises a share of the activation blocks; the CTA that finishes last
+// routes all tokens and builds the plan.
+// ------------------------------------------------------------------------
+constexpr int ROUTER_TPB = 4;      // tokens per CTA
+constexpr int ROUTER_THREADS = 256;
+constexpr int ROUTER_MAXV = 8;     // float4 per thread: rows up to 8192 elements
+
+__global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const RouterArgs a) {
+    extern __shared__ __align__(16) uint8_t dyn[];
+    __shared__ unsigned s_ticket;
+    __shared__ float s_part[ROUTER_THREADS / 32][ROUTER_TPB];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int NW = ROUTER_THREADS / 32;
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+
+    const int e = blockIdx.x % a.E, tg = blockIdx.x / a.E;
+    const int t0 = tg * ROUTER_TPB;
+    const int nv = a.D / 4;  // float4 per row
+    if (t0 < a.T) {
+        const float4 *wrow = reinterpret_cast<const float4 *>(a.wr + (size_t)e * a.D);
+        float4 w[ROUTER_MAXV];
+#pragma unroll
+        for (int i = 0; i < ROUTER_MAXV; ++i) {
+            const int d = tid + i * ROUTER_THREADS;
+            w[i] = d < nv ? __ldg(wrow + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float acc[ROUTER_TPB];
+#pragma unroll
+        for (int tt = 0; tt < ROUTER_TPB; ++tt) {
+            acc[tt] = 0.f;
+            const int t = t0 + tt;
+            if (t < a.T) {
+                const float4 *xr = reinterpret_cast<const float4 *>(a.x + (size_t)t * a.D);
+                float4 v[ROUTER_MAXV];
+#pragma unroll
+                for (int i = 0; i < ROUTER_MAXV; ++i) {
+                    const int d = tid + i * ROUTER_THREADS;
+                    v[i] = d < nv ? xr[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int i = 0; i < ROUTER_MAXV; ++i) {
+                    acc[tt] = fmaf(w[i].x, v[i].x, acc[tt]); acc[tt] = fmaf(w[i].y, v[i].y, acc[tt]);
+                    acc[tt] = fmaf(w[i].z, v[i].z, acc[tt]); acc[tt] = fmaf(w[i].w, v[i].w, acc[tt]);
+                }
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < ROUTER_TPB; ++tt) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], off);
+            if (lane == 0) s_part[warp][tt] = acc[tt];
+        }
+        __syncthreads();
+        if (tid < ROUTER_TPB && t0 + tid < a.T) {
+            float sum = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < NW; ++wv) sum += s_part[wv][tid];
+            a.logits[(size_t)(t0 + tid) * a.E + e] = sum;
+        }
+    }
+    const int nb = a.D / QK_K, stride = q8row_stride(a.D);
+    for (int idx = blockIdx.x * NW + warp; idx < a.T * nb; idx += gridDim.x * NW) {
+        const int t = idx / nb, b = idx % nb;
+        quantize_block_q8k(a.x + (size_t)t * a.D + QK_K * b, a.q8x + (size_t)t * stride, a.D, b, lane, a.q8_layout);
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_ticket = atomicAdd(a.ticket, 1u);
+    __syncthreads();
+    if (s_ticket != gridDim.x - 1) return;
+    __threadfence();
+
+    float *prob_s = reinterpret_cast<float *>(dyn) + (size_t)warp * 2 * a.E;
+    float *sel_s = prob_s + a.E;
+    int *cnt_s = reinterpret_cast<int *>(reinterpret_cast<float *>(dyn) + (size_t)2 * NW * a.E);
+    int *pre_s = cnt_s + a.E + 1;
+    RouterSpec sp{a.E, a.K, a.gating, a.normalize, a.weight_scale, a.n_groups, a.n_groups_used};
+    for (int t = warp; t < a.T; t += NW)
+        route_token_warp(sp, a.logits + (size_t)t * a.E, a.logits + (size_t)t * a.E, a.bias,
+                         a.ids + (size_t)t * a.K, a.weights + (size_t)t * a.K, prob_s, sel_s, lane);
+    __syncthreads();
+    PlanOut po{a.plan.hdr, a.plan.active, a.plan.offs, a.plan.slot, a.plan.item_offs_gu, a.plan.item_offs_dn,
+               a.plan.freq, a.nrt_gu, a.nrt_dn};
+    build_plan_cta(a.ids, a.T * a.K, a.E, po, cnt_s, pre_s);
+    if (tid == 0) *a.ticket = 0u;
+}
+
+int launch_router_decode(const RouterArgs &a, cudaStream_t st) {
+    if (a.D / 4 > ROUTER_MAXV * ROUTER_THREADS) return ZMOE_ERR_SHAPE;
+    const size_t smem = (size_t)2 * (ROUTER_THREADS / 32) * a.E * sizeof(float) + (size_t)2 * (a.E + 1) * sizeof(int);
+    if (smem > 200 * 1024) return ZMOE_ERR_SHAPE;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(router_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_done = true;
+    }
+    const long grid = (long)a.E * ((a.T + ROUTER_TPB - 1) / ROUTER_TPB);
+    if (grid > 0x7fffffffL) return ZMOE_ERR_SHAPE;
+    return launch_pdl(router_decode_kernel, dim3((unsigned)grid), dim3(ROUTER_THREADS), smem, st, a) == cudaSuccess
+               ? ZMOE_OK
+               : ZMOE_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------------
+// stand-alone planners
+// ------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) plan_from_ids_kernel(const int32_t *ids, int P, int E, PlanOut po) {
+    extern __shared__ int plan_s[];
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    build_plan_cta(ids, P, E, po, plan_s, plan_s + E + 1);
+}
+
+int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
+                         cudaStream_t st) {
+    PlanOut po{plan.hdr, plan.active, plan.offs, plan.slot, plan.item_offs_gu, plan.item_offs_dn, plan.freq,
+               nrt_gu, nrt_dn};
+    const size_t smem = (size_t)2 * (E + 1) * sizeof(int);
+    if (smem > 48 * 1024) return ZMOE_ERR_SHAPE;
+    return launch_pdl(plan_from_ids_kernel, dim3(1), dim3(1024), smem, st, ids, P, E, po) == cudaSuccess
+               ? ZMOE_OK
+               : ZMOE_ERR_CUDA;
+}
+
+// dense matmul as a one-expert plan: every row of x is a pair of expert 0
+__global__ void plan_dense_kernel(int S, PlanOut po) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < S; i += gridDim.x * blockDim.x) po.slot[i] = i;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        const int items = ((S + MMID_MAXTOK - 1) / MMID_MAXTOK) * po.nrt_gu;
+        po.active[0] = 0;
+        po.offs[0] = 0; po.offs[1] = S;
+        po.item_offs_gu[0] = 0; po.item_offs_gu[1] = items;
+        po.item_offs_dn[0] = 0; po.item_offs_dn[1] = items;
+        po.hdr[0] = 1; po.hdr[1] = items; po.hdr[2] = items; po.hdr[3] = S;
+    }
+}
+
+int launch_plan_dense(int S, const PlanBuffers &plan, int nrt, cudaStream_t st) {
+    PlanOut po{plan.hdr, plan.active, plan.offs, plan.slot, plan.item_offs_gu, plan.item_offs_dn, nullptr, nrt, nrt};
+    const int grid = (S + 255) / 256 < 64 ? (S + 255) / 256 : 64;
+    return launch_pdl(plan_dense_kernel, dim3(grid > 0 ? grid : 1), dim3(256), 0, st, S, po) == cudaSuccess
+               ? ZMOE_OK
+               : ZMOE_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------------
+// Q8_K row quantiser (one warp per super-block) and the test-side repack to
+// ggml's 292-byte blocks
+// ------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const float *x, int ldx, uint8_t *q8, int rows, int I,
+                                                            int layout) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int nb = I / QK_K, stride = q8row_stride(I);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int idx = blockIdx.x * 8 + warp; idx < rows * nb; idx += gridDim.x * 8) {
+        const int r = idx / nb, b = idx % nb;
+        quantize_block_q8k(x + (size_t)r * ldx + QK_K * b, q8 + (size_t)r * stride, I, b, lane, layout);
+    }
+}
+
+int launch_quantize_rows(const float *x, int ldx, uint8_t *q8, int rows, int I, int layout, cudaStream_t st) {
+    if (rows <= 0) return ZMOE_OK;
+    const long blocks = (long)rows * (I / QK_K);
+    long grid = (blocks + 7) / 8;
+    if (grid > 148 * 8) grid = 148 * 8;
+    return launch_pdl(quantize_rows_kernel, dim3((unsigned)grid), dim3(256), 0, st, x, ldx, q8, rows, I, layout) == cudaSuccess
+               ? ZMOE_OK
+               : ZMOE_ERR_CUDA;
+}
+
+__global__ void q8rows_to_blocks_kernel(const uint8_t *q8, uint8_t *blocks, int rows, int I, int layout) {
+    const int nb = I / QK_K, stride = q8row_stride(I);
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * nb) return;
+    const int r = idx / nb, b = idx % nb;
+    const uint8_t *row = q8 + (size_t)r * stride;
+    uint8_t *o = blocks + (size_t)idx * 292;
+    for (int i = 0; i < 4; ++i) o[i] = row[q8row_d_off(I) + 4 * b + i];
+    for (int i = 0; i < 256; ++i) o[4 + i] = row[q8row_elem_off(layout, b, i)];
+    for (int i = 0; i < 32; ++i) o[260 + i] = row[q8row_bs_off(I) + 32 * b + i];
+}
+
+int launch_q8rows_to_blocks(const uint8_t *q8, uint8_t *blocks, int rows, int I, int layout, cudaStream_t st) {
+    const int n = rows * (I / QK_K);
+    if (n <= 0) return ZMOE_OK;
+    q8rows_to_blocks_kernel<<<(n + 127) / 128, 128, 0, st>>>(q8, blocks, rows, I, layout);
+    return cudaPeekAtLastError() == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------------
+// weighted combine in k order (reference models/graph/moe_routed_ggml.hpp:198-215):
+//   out[t,:] = ((w0*y0 + w1*y1) + w2*y2) + ...
+// products and sums are separately rounded, as a MUL node followed by ADD nodes.
+// Pairs with a negative id contribute a zero row, ids >= E a NaN row
+// (reference kernels/quant/kquant_matmul.cu:659-662).
+// ------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) combine_kernel(float *out, const float *y, const float *w, const int32_t *ids,
+                                                      int T, int K, int D, int E, int accumulate) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int D4 = D / 4;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < (long)T * D4; i += (long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / D4), d4 = (int)(i % D4);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < K; ++k) {
+            const int id = ids[t * K + k];
+            const float wk = w[t * K + k];
+            float4 v;
+            if (id < 0) v = make_float4(0.f, 0.f, 0.f, 0.f);
+            else if (id >= E) v = make_float4(nanf(""), nanf(""), nanf(""), nanf(""));
+            else v = reinterpret_cast<const float4 *>(y + ((size_t)t * K + k) * D)[d4];
+            const float4 pr = make_float4(__fmul_rn(wk, v.x), __fmul_rn(wk, v.y), __fmul_rn(wk, v.z), __fmul_rn(wk, v.w));
+            if (k == 0) acc = pr;
+            else acc = make_float4(__fadd_rn(acc.x, pr.x), __fadd_rn(acc.y, pr.y), __fadd_rn(acc.z, pr.z), __fadd_rn(acc.w, pr.w));
+        }
+        float4 *o = reinterpret_cast<float4 *>(out + (size_t)t * D) + d4;
+        if (accumulate) {
+            const float4 c = *o;
+            acc = make_float4(__fadd_rn(c.x, acc.x), __fadd_rn(c.y, acc.y), __fadd_rn(c.z, acc.z), __fadd_rn(c.w, acc.w));
+        }
+        *o = acc;
+    }
+}
+
+int launch_combine(float *out, const float *y, const float *w, const int32_t *ids, int T, int K, int D, int E,
+                   int accumulate, cudaStream_t st) {
+    const long n = (long)T * (D / 4);
+    long grid = (n + 255) / 256;
+    if (grid > 148 * 8) grid = 148 * 8;
+    return launch_pdl(combine_kernel, dim3((unsigned)grid), dim3(256), 0, st, out, y, w, ids, T, K, D, E, accumulate) ==
+                   cudaSuccess
+               ? ZMOE_OK
+               : ZMOE_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------------
+// test hook: per-super-block integer sums through the same unit functions the
+// production kernels use.  grid = rows, 128 threads; weight row r against
+// activation row r.
+// ------------------------------------------------------------------------
+template <int TYPE>
+__global__ void __launch_bounds__(128) block_isums_kernel(const uint8_t *w, const uint8_t *q8, int32_t *isum,
+                                                          int32_t *msum, int I) {
+    extern __shared__ __align__(16) uint8_t sm[];
+    __shared__ __align__(8) uint64_t g_s[TYPE == IQ2_XXS ? 256 : 1], s_s[TYPE == IQ2_XXS ? 128 : 1];
+    constexpr int BB = QTraits<TYPE>::kBytes;
+    const int nb = I / QK_K, rb = nb * BB, qstride = q8row_stride(I);
+    const int r = blockIdx.x;
+    const uint8_t *wrow = w + (size_t)r * rb;
+    const int mis = (int)((size_t)wrow & 15);  // keep the global alignment of the row
+    uint8_t *wdst = sm + mis;
+    uint8_t *qdst = sm + ((rb + 15 + 32) & ~15);
+    int *acc = reinterpret_cast<int *>(qdst + qstride);
+    for (int i = threadIdx.x; i < rb; i += blockDim.x) wdst[i] = wrow[i];
+    for (int i = threadIdx.x; i < qstride; i += blockDim.x) qdst[i] = q8[(size_t)r * qstride + i];
+    for (int i = threadIdx.x; i < 2 * nb; i += blockDim.x) acc[i] = 0;
+    if (TYPE == IQ2_XXS) iq2_fill_tables(g_s, s_s);
+    __syncthreads();
+    Iq2Tables tb{smem_u32(g_s), smem_u32(s_s)};
+    for (int u = threadIdx.x; u < 4 * nb; u += blockDim.x) {
+        UnitAct a;
+        load_unit_act<TYPE>(smem_u32(qdst), I, u, a);
+        int is, ms;
+        float d, dm;
+        unit_dot<TYPE>(smem_u32(wdst) + (u >> 2) * BB, u & 3, a, tb, is, ms, d, dm);
+        atomicAdd(&acc[u >> 2], is);
+        atomicAdd(&acc[nb + (u >> 2)], ms);
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+        isum[(size_t)r * nb + b] = acc[b];
+        msum[(size_t)r * nb + b] = acc[nb + b];
+    }
+}
+
+int launch_block_isums(int type, const void *w, const uint8_t *q8, int32_t *isum, int32_t *msum, int rows, int I,
+                       cudaStream_t st) {
+    if (rows <= 0) return ZMOE_OK;
+    const int nb = I / QK_K, rb = nb * block_bytes(type);
+    const size_t smem = (size_t)((rb + 15 + 32) & ~15) + q8row_stride(I) + (size_t)2 * nb * sizeof(int) + 16;
+    if (smem > 48 * 1024) return ZMOE_ERR_SHAPE;
+    const uint8_t *wb = static_cast<const uint8_t *>(w);
+    switch (type) {
+    case Q2_K: block_isums_kernel<Q2_K><<<rows, 128, smem, st>>>(wb, q8, isum, msum, I); break;
+    case Q3_K: block_isums_kernel<Q3_K><<<rows, 128, smem, st>>>(wb, q8, isum, msum, I); break;
+    case Q4_K: block_isums_kernel<Q4_K><<<rows, 128, smem, st>>>(wb, q8, isum, msum, I); break;
+    case IQ2_XXS: block_isums_kernel<IQ2_XXS><<<rows, 128, smem, st>>>(wb, q8, isum, msum, I); break;
+    default: return ZMOE_ERR_TYPE;
+    }
+    return cudaPeekAtLastError() == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+}
+
+}  // namespace zmoe
+
+// ------------------------------------------------------------------------
+// reference kernel-launch ABI: element-wise and router entry points
+// ------------------------------------------------------------------------
+namespace {
+
+// reference kernels/math/expert_activation.cu:31-59
+__global__ void expert_swiglu_kernel(float *__restrict__ prod, const float *__restrict__ gate,
+                                     const float *__restrict__ up, int n, float clamp, int fused,
+                                     int *__restrict__ bad) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g0 = gate[i], u0 = up[i];
+    if (bad) {
+        if (isnan(g0) || isnan(u0)) atomicAdd(&bad[0], 1);
+        else if (isinf(g0) || isinf(u0)) atomicAdd(&bad[1], 1);
+    }
+    prod[i] = zmoe::swiglu_f(g0, u0, clamp, fused);
+}
+
+// reference kernels/math/expert_accum.cu:22-37: dst[tok[i],:] += w[i]*src[i,:]; rows of
+// one call target distinct tokens, calls are ordered by the stream
+__global__ void expert_scatter_accum_kernel(const float *__restrict__ src, const int *__restrict__ tok,
+                                            const float *__restrict__ w, float *__restrict__ dst, int n, int D, int S) {
+    const int i = blockIdx.x;
+    if (i >= n) return;
+    const int s = tok[i];
+    if (s < 0 || s >= S) return;
+    const float wt = w ? w[i] : 1.0f;
+    const float *sr = src + (size_t)i * D;
+    float *ds = dst + (size_t)s * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) ds[d] += wt * sr[d];
+}
+
+// reference kernels/models/glm5next_router.cu:33-93, one warp per token
+__global__ void __launch_bounds__(128) router_topk_kernel(float *logits, const float *bias, int32_t *ids,
+                                                          float *weights, int S, zmoe::RouterSpec sp) {
+    extern __shared__ float rs[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= S) return;
+    float *prob_s = rs + (size_t)warp * 2 * sp.E;
+    zmoe::route_token_warp(sp, logits + (size_t)t * sp.E, logits + (size_t)t * sp.E, bias, ids + (size_t)t * sp.K,
+                           weights + (size_t)t * sp.K, prob_s, prob_s + sp.E, lane);
+}
+
+}  // namespace
+
+extern "C" {
+
+void launch_expert_swiglu(float *prod, const float *gate, const float *up, int n, float clamp, int fused, int *d_bad,
+                          void *stream) {
+    if (n <= 0) return;
+    expert_swiglu_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(prod, gate, up, n, clamp, fused, d_bad);
+}
+
+void launch_expert_scatter_accum(const float *src, const int *tok, const float *w, float *dst, int n, int D, int S,
+                                 void *stream) {
+    if (n <= 0 || D <= 0) return;
+    expert_scatter_accum_kernel<<<n, D < 256 ? 64 : 256, 0, static_cast<cudaStream_t>(stream)>>>(src, tok, w, dst, n, D, S);
+}
+
+void launch_expert_scatter_add(const float *src, const int *tok, float *dst, int n, int D, int S,
+                               void *stream) {
+    if (n <= 0 || D <= 0) return;
+    expert_scatter_accum_kernel<<<n, D < 256 ? 64 : 256, 0, static_cast<cudaStream_t>(stream)>>>(src, tok, nullptr, dst, n, D, S);
+}
+
+void launch_glm5next_router_topk(float *logits, const float *bias, int32_t *ids, float *weights, int S, int n_experts,
+                                 int topk, int gating_func, int normalize, float weight_scale, void *stream) {
+    if (S <= 0 || n_experts <= 0 || topk <= 0 || topk > n_experts) return;
+    zmoe::RouterSpec sp{n_experts, topk, gating_func, normalize, weight_scale, 0, 0};
+    const size_t smem = (size_t)8 * n_experts * sizeof(float);
+    if (smem > 48 * 1024) return;
+    router_topk_kernel<<<(S + 3) / 4, 128, smem, static_cast<cudaStream_t>(stream)>>>(logits, bias, ids, weights, S, sp);
+}
+
+}  // extern "C"

@@ -1,0 +1,286 @@
+// mmid.cuh -- the decode-shaped MUL_MAT_ID kernel: quantised expert rows
+// against Q8_K activations, one persistent CTA per SM.
+//
+// Replaces, for decode-shaped calls, the per-(expert, projection) launches of
+// reference core/gpu_expert_executor.cpp:358-387,512-513 and the
+// native_f32_matmul_id kernel of reference kernels/quant/kquant_matmul.cu:647-700.
+//
+// Structure (memory-bound, so everything serves keeping HBM requests in flight):
+//   * work item = (expert, tile of R consecutive weight rows, chunk of <= MAXTOK
+//     pairs routed to that expert).  Rows of one expert are contiguous, so a
+//     tile is ONE contiguous byte range.
+//   * a producer warp streams items through an NSTAGE ring in shared memory
+//     with 1-D bulk asynchronous copies (TMA engine), completion on mbarriers;
+//     the packed Q8_K rows of the item's pairs ride in the same stage.
+//   * consumer warps decode from shared memory.  A row is split over LPR lanes,
+//     each lane owns UPL "units" (64 elements) whose activation words stay in
+//     registers across rows; dot products are dp4a, reduced by warp shuffles.
+//   * DUAL mode reads a gate tile and an up tile and writes SwiGLU(gate, up)
+//     (reference kernels/math/expert_activation.cu:31-59).
+// Every wait is bounded; on expiry the CTA raises an error flag and unwinds.
+#pragma once
+
+#include "quant_units.cuh"
+
+namespace zmoe {
+
+constexpr int MMID_MAXTOK = 4;   // pairs per item
+constexpr int MMID_MAXSTAGE = 6;
+
+// Routing plan produced on the device (router.cu): CSR of pairs by expert and
+// the item index space of the two projections.
+struct PlanView {
+    const int *hdr;        // [0]=n_active [1]=items_gu [2]=items_dn [3]=n_pairs_valid
+    const int *active;     // [n_active] expert ids, ascending
+    const int *offs;       // [E+1]
+    const int *slot;       // [P] pair index t*K+k grouped by expert
+    const int *item_offs;  // [n_active+1] prefix of item counts for THIS projection
+};
+
+struct MmidParams {
+    const uint8_t *w0, *w1;     // weight tensors (w1: up, DUAL only)
+    size_t stride0, stride1;    // bytes between experts
+    size_t total0, total1;      // bytes addressable from w0 / w1
+    int I, O;                   // elements per row, rows per expert
+    int rb;                     // bytes per weight row
+    int R;                      // rows per tile
+    const uint8_t *q8;          // packed activation rows
+    int q8_stride;              // bytes per packed row
+    int xdiv;                   // activation row of pair p is p / xdiv
+    float *y;                   // output [pair][ldy]
+    int ldy;
+    PlanView plan;
+    int hdr_items;              // which hdr slot holds this projection's item count
+    float clamp;
+    int clamp_fused;
+    int nstage;
+    int stage_bytes;            // bytes per ring stage (multiple of 128)
+    int wtile_bytes;            // bytes reserved per weight tile inside a stage (multiple of 128)
+    int *err;                   // device error flag
+};
+
+struct StageMeta {
+    int expert, r0, nrows, ntok;
+    int w0_off, w1_off;   // byte offset of the first row inside the stage
+    int pair[MMID_MAXTOK];
+    int pad[2];
+};
+static_assert(sizeof(StageMeta) == 48, "meta");
+
+__device__ __forceinline__ float swiglu_f(float g, float u, float clamp, int fused) {
+    // reference kernels/math/expert_activation.cu:46-58 (expf, not the fast intrinsic)
+    float out;
+    if (fused) {
+        if (clamp > 0.0f) {
+            g = fminf(g, clamp);
+            u = fmaxf(-clamp, fminf(clamp, u));
+        }
+        out = g / (1.0f + expf(-g)) * u;
+    } else {
+        g = g / (1.0f + expf(-g));
+        out = g * u;
+        if (clamp > 0.0f) out = fmaxf(-clamp, fminf(clamp, out));
+    }
+    return out;
+}
+
+// issue the copy of one weight tile; returns bytes that will complete on `bar`
+__device__ __forceinline__ uint32_t issue_tile(uint8_t *dst, const uint8_t *w, size_t total, size_t g0, size_t g1,
+                                               uint64_t *bar, int *off_out) {
+    const size_t c0 = g0 & ~(size_t)15;
+    size_t c1 = (g1 + 15) & ~(size_t)15;
+    const size_t lim = total & ~(size_t)15;
+    *off_out = (int)(g0 - c0);
+    uint32_t bytes = 0;
+    if (c1 > lim) {
+        // ragged end of the tensor: the last <16 bytes come by plain loads
+        for (size_t i = lim > c0 ? lim : c0; i < g1; ++i) dst[i - c0] = w[i];
+        c1 = lim;
+    }
+    if (c1 > c0) {
+        bytes = (uint32_t)(c1 - c0);
+        bulk_g2s(dst, w + c0, bytes, bar);
+    }
+    return bytes;
+}
+
+template <int TYPE, int LPR, int UPL, bool DUAL, int NCW>
+__global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParams p) {
+    constexpr int BB = QTraits<TYPE>::kBytes;
+    constexpr int RPW = 32 / LPR;  // rows a warp handles at once
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[MMID_MAXSTAGE], empty_bar[MMID_MAXSTAGE];
+    __shared__ StageMeta meta[MMID_MAXSTAGE];
+    __shared__ __align__(8) uint64_t iq2_grid[TYPE == IQ2_XXS ? 256 : 1], iq2_sign[TYPE == IQ2_XXS ? 128 : 1];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nstage = p.nstage;
+    if (tid == 0) {
+        for (int s = 0; s < nstage; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], NCW);
+        }
+        mbar_init_fence();
+    }
+    if (TYPE == IQ2_XXS) iq2_fill_tables(iq2_grid, iq2_sign);
+    __syncthreads();
+
+    // everything below reads what earlier kernels of the stream wrote
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+
+    const int n_items = p.plan.hdr[p.hdr_items];
+    const int n_active = p.plan.hdr[0];
+    // items are dealt round-robin: an item's cost grows with the number of pairs of its
+    // expert, and a strided deal gives every CTA the same mix of experts
+    const int G = (int)gridDim.x;
+    const int n_mine = n_items > (int)blockIdx.x ? (n_items - (int)blockIdx.x + G - 1) / G : 0;
+    const int U = p.I / 64;  // units per row
+    const int nrt = (p.O + p.R - 1) / p.R;
+
+    if (warp == NCW) {
+        // ------------------------------ producer ------------------------------
+        // Item descriptors are resolved 32 at a time, one per lane, so the dependent
+        // global loads of the plan overlap; issuing an item then touches no global
+        // memory except the copies themselves.
+        bool alive = true;
+        for (int batch = 0; batch < n_mine && alive; batch += 32) {
+            const int mine = (int)blockIdx.x + (batch + lane) * G;  // global item index
+            int e = 0, r0 = 0, nrows = 0, ntok = 0, pr[MMID_MAXTOK];
+#pragma unroll
+            for (int t = 0; t < MMID_MAXTOK; ++t) pr[t] = 0;
+            if (batch + lane < n_mine) {
+                int lo = 0, hi = n_active - 1;  // last a with item_offs[a] <= mine
+                while (lo < hi) {
+                    const int mid = (lo + hi + 1) >> 1;
+                    if (p.plan.item_offs[mid] <= mine) lo = mid; else hi = mid - 1;
+                }
+                e = p.plan.active[lo];
+                const int local = mine - p.plan.item_offs[lo];
+                const int tc = local / nrt, rt = local % nrt;
+                r0 = rt * p.R;
+                nrows = min(p.R, p.O - r0);
+                const int s0 = p.plan.offs[e] + tc * MMID_MAXTOK;
+                ntok = min(MMID_MAXTOK, p.plan.offs[e + 1] - s0);
+#pragma unroll
+                for (int t = 0; t < MMID_MAXTOK; ++t)
+                    if (t < ntok) pr[t] = p.plan.slot[s0 + t];
+            }
+            const int nb = min(32, n_mine - batch);
+            for (int j = 0; j < nb; ++j) {
+                const int k = batch + j, s = k % nstage;
+                if (k >= nstage) {
+                    if (!mbar_wait(&empty_bar[s], ((k / nstage) - 1) & 1)) {
+                        if (lane == 0) atomicExch(p.err, 1);
+                        alive = false;
+                        break;
+                    }
+                }
+                const int je = __shfl_sync(0xffffffffu, e, j), jr0 = __shfl_sync(0xffffffffu, r0, j);
+                const int jnrows = __shfl_sync(0xffffffffu, nrows, j), jntok = __shfl_sync(0xffffffffu, ntok, j);
+                int my_pair = 0;
+#pragma unroll
+                for (int t = 0; t < MMID_MAXTOK; ++t) {
+                    const int v = __shfl_sync(0xffffffffu, pr[t], j);
+                    if (lane == t) my_pair = v;
+                }
+                uint8_t *stage = smem + (size_t)s * p.stage_bytes;
+                uint8_t *q8dst = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
+                uint32_t bytes = 0;
+                if (lane == 0) {
+                    StageMeta &m = meta[s];
+                    m.expert = je; m.r0 = jr0; m.nrows = jnrows; m.ntok = jntok;
+                    const size_t g0 = (size_t)je * p.stride0 + (size_t)jr0 * p.rb;
+                    // the producer's own arrival (below, with the byte count) is what lets the
+                    // phase complete, so copies issued before it cannot end the phase early
+                    bytes += issue_tile(stage, p.w0, p.total0, g0, g0 + (size_t)jnrows * p.rb, &full_bar[s], &m.w0_off);
+                    if (DUAL) {
+                        const size_t h0 = (size_t)je * p.stride1 + (size_t)jr0 * p.rb;
+                        bytes += issue_tile(stage + p.wtile_bytes, p.w1, p.total1, h0, h0 + (size_t)jnrows * p.rb,
+                                            &full_bar[s], &m.w1_off);
+                    }
+                }
+                // pairs and their activation rows: one lane per pair
+                if (lane < jntok) {
+                    meta[s].pair[lane] = my_pair;
+                    bulk_g2s(q8dst + (size_t)lane * p.q8_stride, p.q8 + (size_t)(my_pair / p.xdiv) * p.q8_stride,
+                             (uint32_t)p.q8_stride, &full_bar[s]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], bytes + (uint32_t)(jntok * p.q8_stride));
+            }
+        }
+    } else {
+        // ------------------------------ consumers -----------------------------
+        Iq2Tables tb;
+        tb.grid = smem_u32(iq2_grid);
+        tb.signs = smem_u32(iq2_sign);
+        const int sl = lane % LPR, grp = lane / LPR;
+        UnitAct act[UPL];
+        int cached_row = -1;
+        bool ok = true;
+        for (int k = 0; k < n_mine && ok; ++k) {
+            const int s = k % nstage;
+            if (!mbar_wait(&full_bar[s], (k / nstage) & 1)) {
+                if (lane == 0) atomicExch(p.err, 2);
+                ok = false;
+                break;
+            }
+            const StageMeta m = meta[s];
+            const uint32_t stage = smem_u32(smem + (size_t)s * p.stage_bytes);
+            const uint32_t t0 = stage + m.w0_off;
+            const uint32_t t1 = stage + p.wtile_bytes + m.w1_off;
+            const uint32_t q8base = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
+            for (int tk = 0; tk < m.ntok; ++tk) {
+                const int pair = m.pair[tk];
+                const int xrow = pair / p.xdiv;
+                if (xrow != cached_row) {
+#pragma unroll
+                    for (int i = 0; i < UPL; ++i) {
+                        const int u = sl + LPR * i;
+                        if (u < U) load_unit_act<TYPE>(q8base + tk * p.q8_stride, p.I, u, act[i]);
+                    }
+                    cached_row = xrow;
+                }
+                for (int base = warp * RPW; base < m.nrows; base += NCW * RPW) {
+                    const int rr = base + grp;
+                    const bool valid = rr < m.nrows;
+                    float acc0 = 0.f, acc1 = 0.f;
+                    if (valid) {
+#pragma unroll
+                        for (int i = 0; i < UPL; ++i) {
+                            const int u = sl + LPR * i;
+                            if (u < U) {
+                                int is, ms;
+                                float d, dm;
+                                const uint32_t boff = (uint32_t)rr * p.rb + (uint32_t)(u >> 2) * BB;
+                                unit_dot<TYPE>(t0 + boff, u & 3, act[i], tb, is, ms, d, dm);
+                                acc0 = fmaf(d * act[i].d, (float)is, acc0);
+                                if (QTraits<TYPE>::kHasMin) acc0 = fmaf(-(dm * act[i].d), (float)ms, acc0);
+                                if (DUAL) {
+                                    unit_dot<TYPE>(t1 + boff, u & 3, act[i], tb, is, ms, d, dm);
+                                    acc1 = fmaf(d * act[i].d, (float)is, acc1);
+                                    if (QTraits<TYPE>::kHasMin) acc1 = fmaf(-(dm * act[i].d), (float)ms, acc1);
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int off = LPR / 2; off > 0; off >>= 1) {
+                        acc0 += __shfl_xor_sync(0xffffffffu, acc0, off);
+                        if (DUAL) acc1 += __shfl_xor_sync(0xffffffffu, acc1, off);
+                    }
+                    if (valid && sl == 0) {
+                        if (TYPE == IQ2_XXS) { acc0 *= 0.125f; acc1 *= 0.125f; }
+                        const float out = DUAL ? swiglu_f(acc0, acc1, p.clamp, p.clamp_fused) : acc0;
+                        p.y[(size_t)pair * p.ldy + m.r0 + rr] = out;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[s]);
+        }
+    }
+}
+
+}  // namespace zmoe

@@ -1,0 +1,211 @@
+// quant_units.cuh -- integer dot products of quantised weight "units" against
+// Q8_K activations, one unit = 64 of the 256 elements of a super-block.
+//
+// A unit is the grain a lane owns: 16 weight/activation word pairs -> 16 dp4a.
+// Which 64 elements form a unit depends on how the format packs its quants:
+//   planar (Q2_K, Q3_K): unit (n,h) = bytes 16h..16h+15 of the 32-byte group n,
+//       i.e. elements 128n + 32j + 16h + i for j<4, i<16  (four 16-element
+//       scale groups 8n+2j+h).  Layouts: reference kernels/quant/kquant_matmul.cu:55-72,179-199.
+//   linear (Q4_K, IQ2_XXS): unit c = elements 64c .. 64c+63.
+//       Layouts: reference kernels/quant/kquant_matmul.cu:74-92, kernels/quant/iq2_matmul.cu:73-91.
+// Integer sums are exact, so a super-block's isum/msum is the sum over its four
+// units whatever the lane order; only the f32 assembly order differs from the
+// CPU path.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "zmoe_common.cuh"
+
+namespace zmoe {
+
+template <int TYPE> struct QTraits;
+template <> struct QTraits<Q2_K> { static constexpr int kBytes = 84, kAlign = 4; static constexpr bool kPlanar = true, kHasMin = true; };
+template <> struct QTraits<Q3_K> { static constexpr int kBytes = 110, kAlign = 2; static constexpr bool kPlanar = true, kHasMin = false; };
+template <> struct QTraits<Q4_K> { static constexpr int kBytes = 144, kAlign = 16; static constexpr bool kPlanar = false, kHasMin = true; };
+template <> struct QTraits<IQ2_XXS> { static constexpr int kBytes = 66, kAlign = 2; static constexpr bool kPlanar = false, kHasMin = false; };
+
+// activation side of one unit, held in registers
+struct UnitAct {
+    int q[16];   // planar: q[4*j+m]; linear: 16 consecutive words
+    int bs[4];   // planar: bsum of group j; Q4_K: bs[0], bs[1] = bsums of the low / high 32 elements
+    float d;     // Q8_K scale of the unit's super-block
+};
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// Load the activation words unit u (block b = u>>2, sub = u&3) needs from a
+// packed activation row that sits in shared memory at `row` (16-byte aligned).
+template <int TYPE>
+__device__ __forceinline__ void load_unit_act(uint32_t row, int I, int u, UnitAct &a) {
+    const int b = u >> 2, sub = u & 3;
+    a.d = __uint_as_float(lds32(row + q8row_d_off(I) + 4 * b));
+    const uint32_t bs = row + q8row_bs_off(I) + 32 * b;
+    const uint32_t base = row + Q8_UNIT_STRIDE * u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint4 v = lds128(base + 16 * j);
+        a.q[4 * j + 0] = v.x; a.q[4 * j + 1] = v.y; a.q[4 * j + 2] = v.z; a.q[4 * j + 3] = v.w;
+    }
+    if (QTraits<TYPE>::kPlanar) {
+        const int n = sub >> 1, h = sub & 1;
+        const uint4 w = lds128(bs + 16 * n);  // bsums[8n .. 8n+7]; group 8n+2j+h is half h of word j
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a.bs[j] = h ? ((int)ww[j] >> 16) : (int)(short)(ww[j] & 0xffffu);
+    } else {
+        if (TYPE == Q4_K) {
+            const uint2 w = lds64(bs + 8 * sub);  // bsums[4c .. 4c+3]
+            a.bs[0] = (int)(short)(w.x & 0xffffu) + ((int)w.x >> 16);
+            a.bs[1] = (int)(short)(w.y & 0xffffu) + ((int)w.y >> 16);
+        }
+    }
+}
+
+// IQ2_XXS tables in shared memory: 256 x u64 magnitudes, then 128 x u64 byte
+// masks (0xFF where the element is negated).
+struct Iq2Tables {
+    uint32_t grid;   // shared address of uint64_t[256]
+    uint32_t signs;  // shared address of uint64_t[128]
+};
+
+// One unit: returns the integer scale-weighted sum and the integer min-weighted
+// sum, and the block's fp16 scales as floats.
+//   contribution to the row = (d * a.d) * isum - (dmin * a.d) * msum     [x 1/8 for IQ2_XXS, applied by the caller]
+template <int TYPE>
+__device__ __forceinline__ void unit_dot(uint32_t blk, int sub, const UnitAct &a, const Iq2Tables &tb,
+                                         int &isum, int &msum, float &d, float &dmin) {
+    constexpr int AL = QTraits<TYPE>::kAlign;
+    isum = 0;
+    msum = 0;
+    dmin = 0.f;
+    if (TYPE == Q2_K) {
+        // scales[16] @0, qs[64] @16, d @80, dmin @82
+        const int n = sub >> 1, h = sub & 1;
+        uint32_t qs[4];
+        lds32xN_any<AL, 4>(blk + 16 + 32 * n + 16 * h, qs);
+        const uint32_t s0 = lds32(blk + 8 * n), s1 = lds32(blk + 8 * n + 4);
+        const uint32_t dd = lds32(blk + 80);
+        d = half_bits_to_float(dd);
+        dmin = half_bits_to_float(dd >> 16);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            // dp4a on the plane left in place: bytes hold q*4^j, the sum is an exact multiple
+            int s = 0;
+#pragma unroll
+            for (int m = 0; m < 4; ++m) s = dp4a_us(qs[m] & (0x03030303u << (2 * j)), a.q[4 * j + m], s);
+            s >>= 2 * j;
+            const uint32_t scb = ((j < 2 ? s0 : s1) >> (8 * (2 * (j & 1) + h))) & 0xffu;
+            isum += (int)(scb & 0xFu) * s;
+            msum += (int)(scb >> 4) * a.bs[j];
+        }
+    } else if (TYPE == Q3_K) {
+        // hmask[32] @0, qs[64] @32, scales[12] @96, d @108
+        const int n = sub >> 1, h = sub & 1;
+        uint32_t qs[4], hm[4], sc[3];
+        lds32xN_any<AL, 4>(blk + 32 + 32 * n + 16 * h, qs);
+        lds32xN_any<AL, 4>(blk + 16 * h, hm);
+        lds32xN_any<AL, 3>(blk + 96, sc);
+        d = half_bits_to_float(lds16(blk + 108));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int s = 0;
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const uint32_t q2 = (qs[m] >> (2 * j)) & 0x03030303u;
+                const uint32_t hb = (hm[m] >> (4 * n + j)) & 0x01010101u;
+                s = dp4a_us(q2 | (hb << 2), a.q[4 * j + m], s);
+            }
+            s -= 4 * a.bs[j];  // q3 = (q2 | hb<<2) - 4
+            // 6-bit scale k = 8n+2j+h: low nibble from bytes 0..7, high two bits from bytes 8..11
+            const int k = 8 * n + 2 * j + h;
+            const uint32_t lowsrc = (k & 4) ? sc[1] : sc[0];
+            uint32_t lo = (lowsrc >> (8 * (k & 3))) & 0xffu;
+            lo = (k < 8) ? (lo & 0xFu) : (lo >> 4);
+            const uint32_t hi = (sc[2] >> (8 * (k & 3) + 2 * (k >> 2))) & 3u;
+            isum += ((int)(lo | (hi << 4)) - 32) * s;
+        }
+    } else if (TYPE == Q4_K) {
+        // d @0, dmin @2, scales[12] @4, qs[128] @16
+        const int c = sub;
+        const uint4 q0 = lds128(blk + 16 + 32 * c), q1 = lds128(blk + 32 + 32 * c);
+        const uint32_t qs[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint32_t dd = lds32(blk);
+        d = half_bits_to_float(dd);
+        dmin = half_bits_to_float(dd >> 16);
+        const uint32_t s0 = lds32(blk + 4), s1 = lds32(blk + 8), s2 = lds32(blk + 12);
+        // pairs j = 2c, 2c+1 (reference kernels/quant/kquant_matmul.cu:41-48)
+        int sc_lo, sc_hi, m_lo, m_hi;
+        if (c < 2) {
+            sc_lo = (s0 >> (16 * c)) & 63;
+            sc_hi = (s0 >> (16 * c + 8)) & 63;
+            m_lo = (s1 >> (16 * c)) & 63;
+            m_hi = (s1 >> (16 * c + 8)) & 63;
+        } else {
+            const int cc = c - 2;  // j-4 = 2cc, 2cc+1
+            const uint32_t a0 = (s2 >> (16 * cc)) & 0xffu, a1 = (s2 >> (16 * cc + 8)) & 0xffu;
+            sc_lo = (int)((a0 & 0xFu) | ((((s0 >> (16 * cc)) & 0xffu) >> 6) << 4));
+            sc_hi = (int)((a1 & 0xFu) | ((((s0 >> (16 * cc + 8)) & 0xffu) >> 6) << 4));
+            m_lo = (int)((a0 >> 4) | ((((s1 >> (16 * cc)) & 0xffu) >> 6) << 4));
+            m_hi = (int)((a1 >> 4) | ((((s1 >> (16 * cc + 8)) & 0xffu) >> 6) << 4));
+        }
+        int slo = 0, shi = 0;
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            slo = dp4a_us(qs[m] & 0x0F0F0F0Fu, a.q[m], slo);
+            shi = dp4a_us((qs[m] >> 4) & 0x0F0F0F0Fu, a.q[8 + m], shi);
+        }
+        isum = sc_lo * slo + sc_hi * shi;
+        msum = m_lo * a.bs[0] + m_hi * a.bs[1];
+    } else {  // IQ2_XXS: d @0, qs[32] u16 @2 ; unit = sub-blocks 2*sub, 2*sub+1
+        uint32_t aux[4];
+        lds32xN_any<AL, 4>(blk + 2 + 16 * sub, aux);
+        d = half_bits_to_float(lds16(blk));
+#pragma unroll
+        for (int ib = 0; ib < 2; ++ib) {
+            const uint32_t a0 = aux[2 * ib], a1 = aux[2 * ib + 1];
+            int s = 0;
+#pragma unroll
+            for (int l = 0; l < 4; ++l) {
+                const uint2 g = lds64(tb.grid + 8 * ((a0 >> (8 * l)) & 255u));
+                const uint2 neg = lds64(tb.signs + 8 * ((a1 >> (7 * l)) & 127u));
+                const int x0 = a.q[8 * ib + 2 * l], x1 = a.q[8 * ib + 2 * l + 1];
+                // sum(g*sign*x) = sum(g*x) - 2*sum over negated bytes
+                s = dp4a_us(g.x, x0, s);
+                s = dp4a_us(g.y, x1, s);
+                s -= 2 * dp4a_us(g.x & neg.x, x0, dp4a_us(g.y & neg.y, x1, 0));
+            }
+            isum += (int)(2 * (a1 >> 28) + 1) * s;
+        }
+    }
+}
+
+// IQ2_XXS codebook (ggml data; reference backends/cpu/ggml_grids.cpp:11-15)
+static __device__ const uint64_t k_iq2xxs_grid[256] = {
+#include "iq2xxs_grid.inc"
+};
+
+// Fill the IQ2_XXS tables in shared memory from the codebook.  Every thread of
+// the CTA must call it; the caller synchronises afterwards.
+__device__ __forceinline__ void iq2_fill_tables(uint64_t *grid_smem, uint64_t *sign_smem) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) grid_smem[i] = k_iq2xxs_grid[i];
+    for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+        // sign byte = index with bit 7 chosen for even parity; expand bits to 0x00 / 0xFF bytes
+        const uint32_t s = (uint32_t)i | ((uint32_t)(__popc(i) & 1) << 7);
+        uint64_t m = 0;
+        for (int j = 0; j < 8; ++j)
+            if ((s >> j) & 1u) m |= 0xffull << (8 * j);
+        sign_smem[i] = m;
+    }
+}
+
+}  // namespace zmoe

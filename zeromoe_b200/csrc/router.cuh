@@ -1,0 +1,195 @@
+// router.cuh -- router top-k, token-to-expert grouping and the device-side
+// work plan.
+//
+// Follows reference core/moe_router.cpp:6-37 (gating), core/moe_router_service.cpp:1409-1474
+// (selection bias, group-limited routing, top-k, unbiased weight gather,
+// normalise with the 6.103515625e-5 clamp, scale) and
+// kernels/models/glm5next_router.cu:60-92 (lowest index wins ties).
+// Grouping follows reference core/batched_dispatch_pipeline.cpp:1185-1204
+// (offs[e+1] = offs[e] + freq[e]; slot[] holds pair indices t*K+k in
+// token-major order inside each expert).
+#pragma once
+
+#include <math_constants.h>
+
+#include "mmid.cuh"
+
+namespace zmoe {
+
+struct RouterSpec {
+    int E, K;
+    int gating;        // 0 softmax, 1 sigmoid, 2 sqrt(softplus)
+    int normalize;
+    float weight_scale;
+    int n_groups, n_groups_used;
+};
+
+struct PlanOut {
+    int *hdr;          // [4]
+    int *active;       // [E]
+    int *offs;         // [E+1]
+    int *slot;         // [P]
+    int *item_offs_gu; // [E+1]
+    int *item_offs_dn; // [E+1]
+    int *freq;         // [E] expert histogram (reference scratch.expert_freq), may be null
+    int nrt_gu, nrt_dn;  // row tiles per expert of the two projections
+};
+
+__device__ __forceinline__ float gate_scalar(float x, int gating) {
+    if (gating == 1) return 1.0f / (1.0f + expf(-x));
+    const float sp = x > 0.0f ? x + log1pf(expf(-x)) : log1pf(expf(x));
+    return sqrtf(sp);
+}
+
+// (value, index) arg-max over a warp; ties go to the lower index
+__device__ __forceinline__ void warp_argmax(float &v, int &i) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, off);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+}
+
+// One warp routes one token.  row: logits in (global), probs out (global, may
+// alias row).  prob_s / sel_s: per-warp shared scratch of E floats each.
+__device__ void route_token_warp(const RouterSpec &sp, const float *row_in, float *probs_out, const float *bias,
+                                 int32_t *ids, float *weights, float *prob_s, float *sel_s, int lane) {
+    const int E = sp.E, K = sp.K;
+    if (sp.gating == 0) {
+        float mx = -CUDART_INF_F;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row_in[e]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        for (int e = lane; e < E; e += 32) prob_s[e] = expf(row_in[e] - mx);
+        __syncwarp();
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) sum += prob_s[e];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) prob_s[e] *= inv;
+    } else {
+        for (int e = lane; e < E; e += 32) prob_s[e] = gate_scalar(row_in[e], sp.gating);
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) {
+        const float pr = prob_s[e];
+        if (probs_out) probs_out[e] = pr;
+        sel_s[e] = pr + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    // group-limited routing: keep the n_groups_used groups with the largest top-2 sum
+    if (sp.n_groups > 1 && sp.n_groups_used > 0 && sp.n_groups_used < sp.n_groups && E % sp.n_groups == 0 &&
+        sp.n_groups <= 32) {
+        const int G = sp.n_groups, gs = E / G;
+        float score = -CUDART_INF_F;
+        if (lane < G) {
+            float first = -CUDART_INF_F, second = -CUDART_INF_F;
+            for (int j = 0; j < gs; ++j) {
+                const float s = sel_s[lane * gs + j];
+                if (s > first) { second = first; first = s; }
+                else if (s > second) second = s;
+            }
+            score = first + second;
+        }
+        unsigned keep = 0;
+        bool taken = lane >= G;
+        for (int u = 0; u < sp.n_groups_used; ++u) {
+            // untaken groups compete, -inf scores included; ties go to the lower group
+            float bv = taken ? -CUDART_INF_F : score;
+            int bi = taken ? 0x7fffffff : lane;
+            warp_argmax(bv, bi);
+            if (bi == 0x7fffffff) break;
+            keep |= 1u << bi;
+            if (lane == bi) taken = true;
+        }
+        __syncwarp();
+        for (int e = lane; e < E; e += 32)
+            if (!((keep >> (e / gs)) & 1u)) sel_s[e] = -CUDART_INF_F;
+        __syncwarp();
+    }
+    float sum_w = 0.f;
+    for (int k = 0; k < K; ++k) {
+        float bv = -CUDART_INF_F;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float s = sel_s[e];
+            // taken entries are NaN; the first untaken entry is a candidate even at -inf
+            if (!isnan(s) && (bi == 0x7fffffff || s > bv)) { bv = s; bi = e; }
+        }
+        warp_argmax(bv, bi);
+        if (bi == 0x7fffffff) bi = 0;
+        const float w = prob_s[bi];
+        if (lane == 0) {
+            ids[k] = bi;
+            weights[k] = w;
+            sel_s[bi] = CUDART_NAN_F;  // taken
+        }
+        sum_w += w;
+        __syncwarp();
+    }
+    if (lane == 0) {
+        if (sp.normalize) {
+            const float inv = 1.0f / fmaxf(sum_w, 6.103515625e-5f);
+            for (int k = 0; k < K; ++k) weights[k] *= inv;
+        }
+        if (sp.weight_scale != 0.0f)
+            for (int k = 0; k < K; ++k) weights[k] *= sp.weight_scale;
+    }
+}
+
+// CSR of pairs by expert plus the item spaces of the projections.  Called by
+// all threads of ONE CTA; cnt_s/pre_s: shared scratch of E+1 ints each.
+// ids: [T*K] (entries outside [0,E) are skipped: negative = inactive route,
+// reference backends/ggml/mmid_route_skip.hpp:60-67).
+__device__ void build_plan_cta(const int32_t *ids, int P, int E, const PlanOut &po, int *cnt_s, int *pre_s) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    for (int e = tid; e <= E; e += nt) cnt_s[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < P; p += nt) {
+        const int e = ids[p];
+        if (e >= 0 && e < E) atomicAdd(&cnt_s[e], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0, na = 0, igu = 0, idn = 0;
+        po.item_offs_gu[0] = 0;
+        po.item_offs_dn[0] = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = cnt_s[e];
+            pre_s[e] = run;
+            po.offs[e] = run;
+            if (po.freq) po.freq[e] = c;
+            if (c > 0) {
+                po.active[na] = e;
+                const int ntc = (c + MMID_MAXTOK - 1) / MMID_MAXTOK;
+                igu += ntc * po.nrt_gu;
+                idn += ntc * po.nrt_dn;
+                ++na;
+                po.item_offs_gu[na] = igu;
+                po.item_offs_dn[na] = idn;
+            }
+            run += c;
+        }
+        po.offs[E] = run;
+        po.hdr[0] = na; po.hdr[1] = igu; po.hdr[2] = idn; po.hdr[3] = run;
+    }
+    __syncthreads();
+    if (P <= 8192) {
+        // stable fill: thread e walks the pairs in order
+        for (int e = tid; e < E; e += nt) {
+            if (cnt_s[e] == 0) continue;
+            int w = pre_s[e];
+            for (int p = 0; p < P; ++p)
+                if (ids[p] == e) po.slot[w++] = p;
+        }
+    } else {
+        for (int p = tid; p < P; p += nt) {
+            const int e = ids[p];
+            if (e >= 0 && e < E) po.slot[atomicAdd(&pre_s[e], 1)] = p;
+        }
+    }
+}
+
+}  // namespace zmoe

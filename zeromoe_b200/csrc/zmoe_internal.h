@@ -1,0 +1,94 @@
+// zmoe_internal.h -- host-side declarations shared by the .cu files of the
+// library (not part of the public C ABI; see include/zmoe_b200.h for that).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/zmoe_b200.h"
+
+namespace zmoe {
+
+
+// device-resident routing plan buffers
+struct PlanBuffers {
+    int *hdr = nullptr, *active = nullptr, *offs = nullptr, *slot = nullptr;
+    int *item_offs_gu = nullptr, *item_offs_dn = nullptr, *freq = nullptr;
+};
+
+struct RouterArgs {
+    const float *x;        // [T, D]
+    const float *wr;       // [E, D]
+    const float *bias;     // [E] or null
+    int T, D, E, K;
+    int gating, normalize;
+    float weight_scale;
+    int n_groups, n_groups_used;
+    float *logits;         // [T, E] scratch; holds probabilities afterwards
+    int32_t *ids;          // [T, K]
+    float *weights;        // [T, K]
+    uint8_t *q8x;          // packed Q8_K rows of x, [T, q8row_stride(D)]
+    int q8_layout;         // unit layout of q8x (that of the gate / up weight format)
+    PlanBuffers plan;
+    int nrt_gu, nrt_dn;
+    unsigned *ticket;      // zero-initialised counter, left at zero
+};
+
+// geometry of one mmid launch, fixed per (type, I, O)
+struct MmidGeom {
+    int lpr, upl, ncw;     // lanes per row, units per lane, consumer warps
+    int R;                 // rows per tile
+    int nstage, stage_bytes, wtile_bytes;
+    size_t smem_bytes;
+};
+int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g);
+
+struct MmidLaunch {
+    int type;
+    bool dual;
+    const void *w0, *w1;
+    size_t stride0, stride1, total0, total1;
+    int I, O;
+    const uint8_t *q8;
+    int xdiv;
+    float *y;
+    int ldy;
+    PlanBuffers plan;
+    bool down;             // use the down-projection item space
+    float clamp;
+    int clamp_fused;
+    int *err;
+    int n_sm;
+};
+int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st);
+
+int launch_router_decode(const RouterArgs &a, cudaStream_t st);
+int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
+                         cudaStream_t st);
+int launch_plan_dense(int S, const PlanBuffers &plan, int nrt, cudaStream_t st);
+int launch_quantize_rows(const float *x, int ldx, uint8_t *q8, int rows, int I, int layout, cudaStream_t st);
+int launch_q8rows_to_blocks(const uint8_t *q8, uint8_t *blocks, int rows, int I, int layout, cudaStream_t st);
+int launch_combine(float *out, const float *y, const float *w, const int32_t *ids, int T, int K, int D, int E,
+                   int accumulate, cudaStream_t st);
+int launch_block_isums(int type, const void *w, const uint8_t *q8, int32_t *isum, int32_t *msum, int rows, int I,
+                       cudaStream_t st);
+
+// launch helper: programmatic dependent launch attribute on every kernel of the chain
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+}  // namespace zmoe

@@ -1,0 +1,265 @@
+"""ctypes binding of libzmoe_b200.so.  Device memory and streams come from
+torch; every compute call goes through the C ABI."""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libzmoe_b200.so")
+
+Q2_K, Q3_K, Q4_K, IQ2_XXS = 10, 11, 12, 16
+BLOCK_BYTES = {Q2_K: 84, Q3_K: 110, Q4_K: 144, IQ2_XXS: 66}
+GGML_F32, GGML_I32 = 0, 26
+
+ERRORS = {0: "OK", -1: "ARG", -2: "TYPE", -3: "SHAPE", -4: "ALIGN", -5: "CUDA", -6: "CAPACITY",
+          -7: "DEVICE_WAIT", -8: "STATE"}
+
+# every symbol include/zmoe_b200.h declares
+EXPORTS = [
+    "launch_q2_K_matmul", "launch_q2_K_matmul_stream", "launch_q3_K_matmul", "launch_q3_K_matmul_stream",
+    "launch_q4_K_matmul", "launch_iq2_xxs_matmul", "launch_expert_swiglu", "launch_expert_scatter_accum",
+    "launch_expert_scatter_add", "launch_glm5next_router_topk", "zmoe_reserve", "zmoe_last_status",
+    "zmoe_f32_quant_hook", "zeromoe_install_f32_quant_graph_hook", "zeromoe_f32_quant_graph_launches",
+    "zmoe_ctx_create", "zmoe_ctx_destroy", "zmoe_layer_create", "zmoe_layer_destroy", "zmoe_route",
+    "zmoe_set_routes", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
+    "zmoe_get_expert_freq", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_check", "zmoe_kernel_launches",
+    "zmoe_quantize_q8_K", "zmoe_block_isums",
+]
+
+
+class ZmoeError(RuntimeError):
+    def __init__(self, code, where):
+        super().__init__("%s failed: ZMOE_ERR_%s (%d)" % (where, ERRORS.get(code, "?"), code))
+        self.code = code
+
+
+class Weight(C.Structure):
+    _fields_ = [("data_dev", C.c_void_p), ("expert_stride", C.c_size_t), ("bytes", C.c_size_t), ("type", C.c_int)]
+
+
+class LayerDesc(C.Structure):
+    _fields_ = [("d_model", C.c_int), ("d_ff", C.c_int), ("n_experts", C.c_int), ("topk", C.c_int),
+                ("gate", Weight), ("up", Weight), ("down", Weight),
+                ("router_w_dev", C.c_void_p), ("router_bias_dev", C.c_void_p),
+                ("gating", C.c_int), ("weights_norm", C.c_int), ("weights_scale", C.c_float),
+                ("n_groups", C.c_int), ("n_groups_used", C.c_int),
+                ("swiglu_clamp", C.c_float), ("swiglu_clamp_fused", C.c_int)]
+
+
+class Tensor(C.Structure):
+    _fields_ = [("type", C.c_int), ("ne", C.c_int64 * 4), ("nb", C.c_size_t * 4), ("data", C.c_void_p)]
+
+
+_lib = None
+
+
+def load():
+    """Load the shared library; raises when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError("libzmoe_b200.so is not built (run `python -m zeromoe_b200.build`); "
+                          "there is no fallback path")
+    L = C.CDLL(LIB_PATH)
+    vp, i, f = C.c_void_p, C.c_int, C.c_float
+    for name in ("launch_q2_K_matmul", "launch_q3_K_matmul", "launch_q4_K_matmul", "launch_iq2_xxs_matmul"):
+        getattr(L, name).argtypes = [vp, vp, vp, i, i, i]
+        getattr(L, name).restype = None
+    for name in ("launch_q2_K_matmul_stream", "launch_q3_K_matmul_stream"):
+        getattr(L, name).argtypes = [vp, vp, vp, i, i, i, vp]
+        getattr(L, name).restype = None
+    L.launch_expert_swiglu.argtypes = [vp, vp, vp, i, f, i, vp, vp]
+    L.launch_expert_swiglu.restype = None
+    L.launch_expert_scatter_accum.argtypes = [vp, vp, vp, vp, i, i, i, vp]
+    L.launch_expert_scatter_accum.restype = None
+    L.launch_expert_scatter_add.argtypes = [vp, vp, vp, i, i, i, vp]
+    L.launch_expert_scatter_add.restype = None
+    L.launch_glm5next_router_topk.argtypes = [vp, vp, vp, vp, i, i, i, i, i, f, vp]
+    L.launch_glm5next_router_topk.restype = None
+    L.zmoe_reserve.argtypes = [i, i]
+    L.zmoe_f32_quant_hook.argtypes = [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor),
+                                      vp, C.c_bool]
+    L.zmoe_f32_quant_hook.restype = C.c_bool
+    L.zeromoe_install_f32_quant_graph_hook.restype = C.c_bool
+    L.zeromoe_f32_quant_graph_launches.restype = C.c_uint64
+    L.zmoe_kernel_launches.restype = C.c_uint64
+    L.zmoe_ctx_create.argtypes = [i, i, i, i, i, C.POINTER(vp)]
+    L.zmoe_ctx_destroy.argtypes = [vp]
+    L.zmoe_ctx_destroy.restype = None
+    L.zmoe_layer_create.argtypes = [vp, C.POINTER(LayerDesc), C.POINTER(vp)]
+    L.zmoe_layer_destroy.argtypes = [vp]
+    L.zmoe_layer_destroy.restype = None
+    L.zmoe_route.argtypes = [vp, vp, i, vp]
+    L.zmoe_set_routes.argtypes = [vp, vp, vp, vp, i, vp]
+    L.zmoe_expert_ffn.argtypes = [vp, vp, i, i, vp]
+    L.zmoe_expert_ffn_events.argtypes = [vp, vp, i, i, vp, vp, vp]
+    L.zmoe_moe_forward.argtypes = [vp, vp, vp, i, vp]
+    L.zmoe_moe_forward_host.argtypes = [vp, vp, vp, i]
+    L.zmoe_get_routes.argtypes = [vp, i, i, vp, vp]
+    L.zmoe_get_expert_freq.argtypes = [vp, i, vp]
+    L.zmoe_get_probs.argtypes = [vp, i, i, vp]
+    L.zmoe_get_act.argtypes = [vp, i, i, vp]
+    L.zmoe_ctx_check.argtypes = [vp]
+    L.zmoe_quantize_q8_K.argtypes = [vp, vp, i, i, i, vp]
+    L.zmoe_block_isums.argtypes = [i, vp, vp, vp, vp, i, i, vp]
+    _lib = L
+    return L
+
+
+def check(rc, where):
+    if rc != 0:
+        raise ZmoeError(rc, where)
+
+
+def _stream_ptr(stream=None):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+class Context:
+    """Per-device scratch (zmoe_ctx)."""
+
+    def __init__(self, max_tokens, max_d_model, max_d_ff, max_experts, max_topk):
+        self.h = C.c_void_p()
+        check(load().zmoe_ctx_create(max_tokens, max_d_model, max_d_ff, max_experts, max_topk, C.byref(self.h)),
+              "zmoe_ctx_create")
+        self.max_tokens = max_tokens
+
+    def check(self):
+        check(load().zmoe_ctx_check(self.h), "zmoe_ctx_check")
+
+    def routes(self, T, K):
+        ids = np.zeros((T, K), dtype=np.int32)
+        w = np.zeros((T, K), dtype=np.float32)
+        check(load().zmoe_get_routes(self.h, T, K, ids.ctypes.data_as(C.c_void_p), w.ctypes.data_as(C.c_void_p)),
+              "zmoe_get_routes")
+        return ids, w
+
+    def expert_freq(self, E):
+        f = np.zeros(E, dtype=np.int32)
+        check(load().zmoe_get_expert_freq(self.h, E, f.ctypes.data_as(C.c_void_p)), "zmoe_get_expert_freq")
+        return f
+
+    def probs(self, T, E):
+        p = np.zeros((T, E), dtype=np.float32)
+        check(load().zmoe_get_probs(self.h, T, E, p.ctypes.data_as(C.c_void_p)), "zmoe_get_probs")
+        return p
+
+    def act(self, P, F):
+        a = np.zeros((P, F), dtype=np.float32)
+        check(load().zmoe_get_act(self.h, P, F, a.ctypes.data_as(C.c_void_p)), "zmoe_get_act")
+        return a
+
+    def close(self):
+        if self.h:
+            load().zmoe_ctx_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Layer:
+    """One MoE layer over borrowed device weights (torch uint8 tensors [E, rows, row_bytes])."""
+
+    def __init__(self, ctx, d_model, d_ff, n_experts, topk, types, w_gate, w_up, w_down, router_w=None,
+                 router_bias=None, gating=0, weights_norm=1, weights_scale=0.0, n_groups=0, n_groups_used=0,
+                 clamp=0.0, clamp_fused=0):
+        self.ctx = ctx
+        self.keep = (w_gate, w_up, w_down, router_w, router_bias)
+        self.d_model, self.d_ff, self.n_experts, self.topk = d_model, d_ff, n_experts, topk
+        d = LayerDesc()
+        d.d_model, d.d_ff, d.n_experts, d.topk = d_model, d_ff, n_experts, topk
+        for wt, t, ty in ((d.gate, w_gate, types[0]), (d.up, w_up, types[1]), (d.down, w_down, types[2])):
+            wt.data_dev = t.data_ptr()
+            wt.expert_stride = t.stride(0) * t.element_size()
+            wt.bytes = 0
+            wt.type = ty
+        d.router_w_dev = router_w.data_ptr() if router_w is not None else None
+        d.router_bias_dev = router_bias.data_ptr() if router_bias is not None else None
+        d.gating, d.weights_norm, d.weights_scale = gating, weights_norm, weights_scale
+        d.n_groups, d.n_groups_used = n_groups, n_groups_used
+        d.swiglu_clamp, d.swiglu_clamp_fused = clamp, clamp_fused
+        self.desc = d
+        self.h = C.c_void_p()
+        check(load().zmoe_layer_create(ctx.h, C.byref(d), C.byref(self.h)), "zmoe_layer_create")
+
+    def route(self, x, stream=None):
+        check(load().zmoe_route(self.h, ptr(x), x.shape[0], _stream_ptr(stream)), "zmoe_route")
+
+    def set_routes(self, x, ids, weights, stream=None):
+        check(load().zmoe_set_routes(self.h, ptr(x), ptr(ids), ptr(weights), x.shape[0], _stream_ptr(stream)),
+              "zmoe_set_routes")
+
+    def expert_ffn(self, out, accumulate=0, stream=None):
+        check(load().zmoe_expert_ffn(self.h, ptr(out), out.shape[0], accumulate, _stream_ptr(stream)),
+              "zmoe_expert_ffn")
+
+    def expert_ffn_timed(self, out, ev0, ev1, stream=None):
+        """expert_ffn with two torch.cuda.Event recorded around the gate/up matmul"""
+        for ev in (ev0, ev1):
+            if not ev.cuda_event:      # torch creates the handle on first record
+                ev.record()
+        check(load().zmoe_expert_ffn_events(self.h, ptr(out), out.shape[0], 0, _stream_ptr(stream),
+                                            C.c_void_p(ev0.cuda_event), C.c_void_p(ev1.cuda_event)),
+              "zmoe_expert_ffn_events")
+
+    def forward(self, x, out, stream=None):
+        check(load().zmoe_moe_forward(self.h, ptr(x), ptr(out), x.shape[0], _stream_ptr(stream)), "zmoe_moe_forward")
+
+    def forward_host(self, x_host, out_host):
+        """x_host / out_host: host tensors or arrays [T, d_model] f32 (pinned for full speed)"""
+        T = x_host.shape[0]
+        xp = x_host.data_ptr() if hasattr(x_host, "data_ptr") else x_host.ctypes.data
+        op = out_host.data_ptr() if hasattr(out_host, "data_ptr") else out_host.ctypes.data
+        check(load().zmoe_moe_forward_host(self.h, C.c_void_p(xp), C.c_void_p(op), T), "zmoe_moe_forward_host")
+
+    def close(self):
+        if self.h:
+            load().zmoe_layer_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def dense_matmul(qtype, x, w, O, stream=None):
+    """y[S,O] = x[S,I] . W^T through the reference's launch_*_matmul symbols (torch tensors on the device)"""
+    import torch
+    S, I = x.shape
+    y = torch.empty((S, O), dtype=torch.float32, device=x.device)
+    L = load()
+    if qtype == Q2_K:
+        L.launch_q2_K_matmul_stream(ptr(y), ptr(x), ptr(w), S, I, O, _stream_ptr(stream))
+    elif qtype == Q3_K:
+        L.launch_q3_K_matmul_stream(ptr(y), ptr(x), ptr(w), S, I, O, _stream_ptr(stream))
+    else:
+        # these two symbols have no stream variant in the reference: legacy default stream
+        torch.cuda.current_stream().synchronize()
+        (L.launch_q4_K_matmul if qtype == Q4_K else L.launch_iq2_xxs_matmul)(ptr(y), ptr(x), ptr(w), S, I, O)
+        torch.cuda.synchronize()
+    check(L.zmoe_last_status(), "launch_*_matmul")
+    return y
+
+
+def make_tensor(t, qtype, ne, nb):
+    T = Tensor()
+    T.type = qtype
+    for k in range(4):
+        T.ne[k] = ne[k]
+        T.nb[k] = nb[k]
+    T.data = t.data_ptr()
+    return T
