@@ -46,13 +46,16 @@ struct PlanStore {
         rc |= dev_alloc(&b.item_offs_gu, E + 1);
         rc |= dev_alloc(&b.item_offs_dn, E + 1);
         rc |= dev_alloc(&b.freq, E);
+        rc |= dev_alloc(&b.aoffs, E);
+        rc |= dev_alloc(&b.antok, E);
+        b.cap_e = E;
         cap_e = E;
         cap_p = P;
         return rc ? ZMOE_ERR_CUDA : ZMOE_OK;
     }
     void release() {
         cudaFree(b.hdr); cudaFree(b.active); cudaFree(b.offs); cudaFree(b.slot);
-        cudaFree(b.item_offs_gu); cudaFree(b.item_offs_dn); cudaFree(b.freq);
+        cudaFree(b.item_offs_gu); cudaFree(b.item_offs_dn); cudaFree(b.freq); cudaFree(b.aoffs); cudaFree(b.antok);
         b = PlanBuffers();
         cap_e = cap_p = 0;
     }

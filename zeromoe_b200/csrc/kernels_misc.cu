@@ -17,6 +17,7 @@ namespace zmoe {
 constexpr int ROUTER_TPB = 4;      // tokens per CTA
 constexpr int ROUTER_THREADS = 256;
 constexpr int ROUTER_MAXV = 8;     // float4 per thread: rows up to 8192 elements
+constexpr int ROUTER_IDS_SMEM = 2048;  // pairs whose ids the planner mirrors in shared memory
 
 __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const RouterArgs a) {
     extern __shared__ __align__(16) uint8_t dyn[];
@@ -88,20 +89,22 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const Rou
     float *sel_s = prob_s + a.E;
     int *cnt_s = reinterpret_cast<int *>(reinterpret_cast<float *>(dyn) + (size_t)2 * NW * a.E);
     int *pre_s = cnt_s + a.E + 1;
+    int *ids_s = a.T * a.K <= ROUTER_IDS_SMEM ? pre_s + a.E + 1 : nullptr;
     RouterSpec sp{a.E, a.K, a.gating, a.normalize, a.weight_scale, a.n_groups, a.n_groups_used};
     for (int t = warp; t < a.T; t += NW)
         route_token_warp(sp, a.logits + (size_t)t * a.E, a.logits + (size_t)t * a.E, a.bias,
                          a.ids + (size_t)t * a.K, a.weights + (size_t)t * a.K, prob_s, sel_s, lane);
     __syncthreads();
     PlanOut po{a.plan.hdr, a.plan.active, a.plan.offs, a.plan.slot, a.plan.item_offs_gu, a.plan.item_offs_dn,
-               a.plan.freq, a.nrt_gu, a.nrt_dn};
-    build_plan_cta(a.ids, a.T * a.K, a.E, po, cnt_s, pre_s);
+               a.plan.freq, a.plan.aoffs, a.plan.antok, a.nrt_gu, a.nrt_dn};
+    build_plan_cta(a.ids, a.T * a.K, a.E, po, cnt_s, pre_s, ids_s);
     if (tid == 0) *a.ticket = 0u;
 }
 
 int launch_router_decode(const RouterArgs &a, cudaStream_t st) {
     if (a.D / 4 > ROUTER_MAXV * ROUTER_THREADS) return ZMOE_ERR_SHAPE;
-    const size_t smem = (size_t)2 * (ROUTER_THREADS / 32) * a.E * sizeof(float) + (size_t)2 * (a.E + 1) * sizeof(int);
+    const size_t smem = (size_t)2 * (ROUTER_THREADS / 32) * a.E * sizeof(float) + (size_t)2 * (a.E + 1) * sizeof(int) +
+                        (a.T * a.K <= ROUTER_IDS_SMEM ? (size_t)a.T * a.K * sizeof(int) : 0);
     if (smem > 200 * 1024) return ZMOE_ERR_SHAPE;
     static bool attr_done = false;
     if (!attr_done) {
@@ -122,14 +125,14 @@ __global__ void __launch_bounds__(1024) plan_from_ids_kernel(const int32_t *ids,
     extern __shared__ int plan_s[];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
-    build_plan_cta(ids, P, E, po, plan_s, plan_s + E + 1);
+    build_plan_cta(ids, P, E, po, plan_s, plan_s + E + 1, P <= ROUTER_IDS_SMEM ? plan_s + 2 * (E + 1) : nullptr);
 }
 
 int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
                          cudaStream_t st) {
     PlanOut po{plan.hdr, plan.active, plan.offs, plan.slot, plan.item_offs_gu, plan.item_offs_dn, plan.freq,
-               nrt_gu, nrt_dn};
-    const size_t smem = (size_t)2 * (E + 1) * sizeof(int);
+               plan.aoffs, plan.antok, nrt_gu, nrt_dn};
+    const size_t smem = (size_t)2 * (E + 1) * sizeof(int) + (P <= ROUTER_IDS_SMEM ? (size_t)P * sizeof(int) : 0);
     if (smem > 48 * 1024) return ZMOE_ERR_SHAPE;
     return launch_pdl(plan_from_ids_kernel, dim3(1), dim3(1024), smem, st, ids, P, E, po) == cudaSuccess
                ? ZMOE_OK
@@ -144,6 +147,7 @@ __global__ void plan_dense_kernel(int S, PlanOut po) {
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         const int items = ((S + MMID_MAXTOK - 1) / MMID_MAXTOK) * po.nrt_gu;
         po.active[0] = 0;
+        po.aoffs[0] = 0; po.antok[0] = S;
         po.offs[0] = 0; po.offs[1] = S;
         po.item_offs_gu[0] = 0; po.item_offs_gu[1] = items;
         po.item_offs_dn[0] = 0; po.item_offs_dn[1] = items;
@@ -152,7 +156,8 @@ __global__ void plan_dense_kernel(int S, PlanOut po) {
 }
 
 int launch_plan_dense(int S, const PlanBuffers &plan, int nrt, cudaStream_t st) {
-    PlanOut po{plan.hdr, plan.active, plan.offs, plan.slot, plan.item_offs_gu, plan.item_offs_dn, nullptr, nrt, nrt};
+    PlanOut po{plan.hdr, plan.active, plan.offs, plan.slot, plan.item_offs_gu, plan.item_offs_dn, nullptr,
+               plan.aoffs, plan.antok, nrt, nrt};
     const int grid = (S + 255) / 256 < 64 ? (S + 255) / 256 : 64;
     return launch_pdl(plan_dense_kernel, dim3(grid > 0 ? grid : 1), dim3(256), 0, st, S, po) == cudaSuccess
                ? ZMOE_OK

@@ -96,9 +96,10 @@ int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
         std::lock_guard<std::mutex> lock(mu);
         size_t &have = done[std::make_pair(reinterpret_cast<const void *>(fn), dev)];
         if (have < g.smem_bytes) {
-            if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 4096) != cudaSuccess)
+            // the budget of mmid_geometry (200 KB) plus the kernel's static arrays stays under 227 KB
+            if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
                 return ZMOE_ERR_CUDA;
-            have = 227 * 1024 - 4096;
+            have = 200 * 1024;
         }
     }
     MmidParams p;
@@ -115,6 +116,7 @@ int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
     p.y = L.y; p.ldy = L.ldy;
     p.plan.hdr = L.plan.hdr; p.plan.active = L.plan.active; p.plan.offs = L.plan.offs; p.plan.slot = L.plan.slot;
     p.plan.item_offs = L.down ? L.plan.item_offs_dn : L.plan.item_offs_gu;
+    p.plan.aoffs = L.plan.aoffs; p.plan.antok = L.plan.antok; p.plan.cap_e = L.plan.cap_e;
     p.hdr_items = L.down ? 2 : 1;
     p.clamp = L.clamp; p.clamp_fused = L.clamp_fused;
     p.nstage = g.nstage; p.stage_bytes = g.stage_bytes; p.wtile_bytes = g.wtile_bytes;

@@ -35,7 +35,11 @@ struct PlanView {
     const int *offs;       // [E+1]
     const int *slot;       // [P] pair index t*K+k grouped by expert
     const int *item_offs;  // [n_active+1] prefix of item counts for THIS projection
+    const int *aoffs;      // [n_active] offs[active[a]]
+    const int *antok;      // [n_active] pairs of active[a]
+    int cap_e;             // capacity of the arrays above
 };
+constexpr int MMID_PLAN_SMEM = 512;  // active experts whose plan rows are mirrored in shared memory
 
 struct MmidParams {
     const uint8_t *w0, *w1;     // weight tensors (w1: up, DUAL only)
@@ -63,9 +67,10 @@ struct StageMeta {
     int expert, r0, nrows, ntok;
     int w0_off, w1_off;   // byte offset of the first row inside the stage
     int pair[MMID_MAXTOK];
+    int xrow[MMID_MAXTOK];  // activation row of each pair
     int pad[2];
 };
-static_assert(sizeof(StageMeta) == 48, "meta");
+static_assert(sizeof(StageMeta) == 64, "meta");
 
 __device__ __forceinline__ float swiglu_f(float g, float u, float clamp, int fused) {
     // reference kernels/math/expert_activation.cu:46-58 (expf, not the fast intrinsic)
@@ -113,6 +118,8 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
     __shared__ StageMeta meta[MMID_MAXSTAGE];
     __shared__ __align__(8) uint64_t iq2_grid[TYPE == IQ2_XXS ? 256 : 1], iq2_sign[TYPE == IQ2_XXS ? 128 : 1];
 
+    __shared__ int s_item_offs[MMID_PLAN_SMEM + 1], s_active[MMID_PLAN_SMEM], s_aoffs[MMID_PLAN_SMEM],
+        s_antok[MMID_PLAN_SMEM];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nstage = p.nstage;
     if (tid == 0) {
@@ -129,8 +136,18 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
     pdl_wait_prior_grid();
     pdl_launch_dependents();
 
+    // one round trip for the whole plan: header and per-expert rows are fetched together
     const int n_items = p.plan.hdr[p.hdr_items];
     const int n_active = p.plan.hdr[0];
+    for (int i = tid; i < MMID_PLAN_SMEM && i < p.plan.cap_e; i += blockDim.x) {
+        s_item_offs[i + 1] = p.plan.item_offs[i + 1];
+        s_active[i] = p.plan.active[i];
+        s_aoffs[i] = p.plan.aoffs[i];
+        s_antok[i] = p.plan.antok[i];
+    }
+    if (tid == 0) s_item_offs[0] = 0;
+    __syncthreads();
+    const bool plan_in_smem = n_active <= MMID_PLAN_SMEM;
     // items are dealt round-robin: an item's cost grows with the number of pairs of its
     // expert, and a strided deal gives every CTA the same mix of experts
     const int G = (int)gridDim.x;
@@ -151,17 +168,26 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
             for (int t = 0; t < MMID_MAXTOK; ++t) pr[t] = 0;
             if (batch + lane < n_mine) {
                 int lo = 0, hi = n_active - 1;  // last a with item_offs[a] <= mine
-                while (lo < hi) {
-                    const int mid = (lo + hi + 1) >> 1;
-                    if (p.plan.item_offs[mid] <= mine) lo = mid; else hi = mid - 1;
+                int local, ebase, ecnt;
+                if (plan_in_smem) {
+                    while (lo < hi) {
+                        const int mid = (lo + hi + 1) >> 1;
+                        if (s_item_offs[mid] <= mine) lo = mid; else hi = mid - 1;
+                    }
+                    e = s_active[lo]; local = mine - s_item_offs[lo]; ebase = s_aoffs[lo]; ecnt = s_antok[lo];
+                } else {
+                    while (lo < hi) {
+                        const int mid = (lo + hi + 1) >> 1;
+                        if (p.plan.item_offs[mid] <= mine) lo = mid; else hi = mid - 1;
+                    }
+                    e = p.plan.active[lo]; local = mine - p.plan.item_offs[lo];
+                    ebase = p.plan.aoffs[lo]; ecnt = p.plan.antok[lo];
                 }
-                e = p.plan.active[lo];
-                const int local = mine - p.plan.item_offs[lo];
                 const int tc = local / nrt, rt = local % nrt;
                 r0 = rt * p.R;
                 nrows = min(p.R, p.O - r0);
-                const int s0 = p.plan.offs[e] + tc * MMID_MAXTOK;
-                ntok = min(MMID_MAXTOK, p.plan.offs[e + 1] - s0);
+                const int s0 = ebase + tc * MMID_MAXTOK;
+                ntok = min(MMID_MAXTOK, ecnt - tc * MMID_MAXTOK);
 #pragma unroll
                 for (int t = 0; t < MMID_MAXTOK; ++t)
                     if (t < ntok) pr[t] = p.plan.slot[s0 + t];
@@ -202,8 +228,10 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
                 }
                 // pairs and their activation rows: one lane per pair
                 if (lane < jntok) {
+                    const int xr = my_pair / p.xdiv;
                     meta[s].pair[lane] = my_pair;
-                    bulk_g2s(q8dst + (size_t)lane * p.q8_stride, p.q8 + (size_t)(my_pair / p.xdiv) * p.q8_stride,
+                    meta[s].xrow[lane] = xr;
+                    bulk_g2s(q8dst + (size_t)lane * p.q8_stride, p.q8 + (size_t)xr * p.q8_stride,
                              (uint32_t)p.q8_stride, &full_bar[s]);
                 }
                 __syncwarp();
@@ -219,6 +247,19 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
         UnitAct act[UPL];
         int cached_row = -1;
         bool ok = true;
+        // finished outputs wait in lane registers (pass n of a row group parks in that group's lane n)
+        // and are finalised LPR passes at a time, so the SwiGLU / store epilogue runs once per LPR passes
+        float park0 = 0.f, park1 = 0.f;
+        size_t park_idx = 0;
+        int parked = 0;
+        auto flush = [&]() {
+            if (sl < parked) {
+                float a0 = park0, a1 = park1;
+                if (TYPE == IQ2_XXS) { a0 *= 0.125f; a1 *= 0.125f; }
+                if (park_idx != (size_t)-1) p.y[park_idx] = DUAL ? swiglu_f(a0, a1, p.clamp, p.clamp_fused) : a0;
+            }
+            parked = 0;
+        };
         for (int k = 0; k < n_mine && ok; ++k) {
             const int s = k % nstage;
             if (!mbar_wait(&full_bar[s], (k / nstage) & 1)) {
@@ -226,14 +267,15 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
                 ok = false;
                 break;
             }
-            const StageMeta m = meta[s];
+            const StageMeta &m = meta[s];
+            const int m_nrows = m.nrows, m_ntok = m.ntok, m_r0 = m.r0;
             const uint32_t stage = smem_u32(smem + (size_t)s * p.stage_bytes);
             const uint32_t t0 = stage + m.w0_off;
             const uint32_t t1 = stage + p.wtile_bytes + m.w1_off;
             const uint32_t q8base = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
-            for (int tk = 0; tk < m.ntok; ++tk) {
+            for (int tk = 0; tk < m_ntok; ++tk) {
                 const int pair = m.pair[tk];
-                const int xrow = pair / p.xdiv;
+                const int xrow = m.xrow[tk];
                 if (xrow != cached_row) {
 #pragma unroll
                     for (int i = 0; i < UPL; ++i) {
@@ -242,9 +284,9 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
                     }
                     cached_row = xrow;
                 }
-                for (int base = warp * RPW; base < m.nrows; base += NCW * RPW) {
+                for (int base = warp * RPW; base < m_nrows; base += NCW * RPW) {
                     const int rr = base + grp;
-                    const bool valid = rr < m.nrows;
+                    const bool valid = rr < m_nrows;
                     float acc0 = 0.f, acc1 = 0.f;
                     if (valid) {
 #pragma unroll
@@ -270,16 +312,18 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
                         acc0 += __shfl_xor_sync(0xffffffffu, acc0, off);
                         if (DUAL) acc1 += __shfl_xor_sync(0xffffffffu, acc1, off);
                     }
-                    if (valid && sl == 0) {
-                        if (TYPE == IQ2_XXS) { acc0 *= 0.125f; acc1 *= 0.125f; }
-                        const float out = DUAL ? swiglu_f(acc0, acc1, p.clamp, p.clamp_fused) : acc0;
-                        p.y[(size_t)pair * p.ldy + m.r0 + rr] = out;
+                    // every lane of a row group now holds the row's sums: the group's lane `parked` keeps them
+                    if (sl == parked) {
+                        park0 = acc0; park1 = acc1;
+                        park_idx = valid ? (size_t)pair * p.ldy + m_r0 + rr : (size_t)-1;
                     }
+                    if (++parked == LPR) flush();
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[s]);
         }
+        flush();
     }
 }
 

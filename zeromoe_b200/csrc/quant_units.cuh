@@ -28,7 +28,8 @@ template <> struct QTraits<IQ2_XXS> { static constexpr int kBytes = 66, kAlign =
 // activation side of one unit, held in registers
 struct UnitAct {
     int q[16];   // planar: q[4*j+m]; linear: 16 consecutive words
-    int bs[4];   // planar: bsum of group j; Q4_K: bs[0], bs[1] = bsums of the low / high 32 elements
+    int bs[2];   // planar: bsums of groups j=0,1 and j=2,3 as packed int16 pairs;
+                 // Q4_K: bs[0], bs[1] = bsums of the low / high 32 elements
     float d;     // Q8_K scale of the unit's super-block
 };
 
@@ -59,9 +60,9 @@ __device__ __forceinline__ void load_unit_act(uint32_t row, int I, int u, UnitAc
     if (QTraits<TYPE>::kPlanar) {
         const int n = sub >> 1, h = sub & 1;
         const uint4 w = lds128(bs + 16 * n);  // bsums[8n .. 8n+7]; group 8n+2j+h is half h of word j
-        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) a.bs[j] = h ? ((int)ww[j] >> 16) : (int)(short)(ww[j] & 0xffffu);
+        const uint32_t sel = h ? 0x7632u : 0x5410u;
+        a.bs[0] = (int)__byte_perm(w.x, w.y, sel);
+        a.bs[1] = (int)__byte_perm(w.z, w.w, sel);
     } else {
         if (TYPE == Q4_K) {
             const uint2 w = lds64(bs + 8 * sub);  // bsums[4c .. 4c+3]
@@ -97,17 +98,20 @@ __device__ __forceinline__ void unit_dot(uint32_t blk, int sub, const UnitAct &a
         const uint32_t dd = lds32(blk + 80);
         d = half_bits_to_float(dd);
         dmin = half_bits_to_float(dd >> 16);
+        // bytes j = scale | min << 4 of groups 8n + 2j + h
+        const uint32_t w4 = __byte_perm(s0, s1, h ? 0x7531u : 0x6420u);
+        const uint32_t sc4 = w4 & 0x0F0F0F0Fu, mn4 = (w4 >> 4) & 0x0F0F0F0Fu;
+        int S[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             // dp4a on the plane left in place: bytes hold q*4^j, the sum is an exact multiple
-            int s = 0;
+            int t = 0;
 #pragma unroll
-            for (int m = 0; m < 4; ++m) s = dp4a_us(qs[m] & (0x03030303u << (2 * j)), a.q[4 * j + m], s);
-            s >>= 2 * j;
-            const uint32_t scb = ((j < 2 ? s0 : s1) >> (8 * (2 * (j & 1) + h))) & 0xffu;
-            isum += (int)(scb & 0xFu) * s;
-            msum += (int)(scb >> 4) * a.bs[j];
+            for (int m = 0; m < 4; ++m) t = dp4a_us(qs[m] & (0x03030303u << (2 * j)), a.q[4 * j + m], t);
+            S[j] = t >> (2 * j);   // |S| <= 16*3*127: fits 16 bits
         }
+        isum = dp2a_hi_su(pack16(S[2], S[3]), sc4, dp2a_lo_su(pack16(S[0], S[1]), sc4, 0));
+        msum = dp2a_hi_su((uint32_t)a.bs[1], mn4, dp2a_lo_su((uint32_t)a.bs[0], mn4, 0));
     } else if (TYPE == Q3_K) {
         // hmask[32] @0, qs[64] @32, scales[12] @96, d @108
         const int n = sub >> 1, h = sub & 1;
@@ -117,23 +121,33 @@ __device__ __forceinline__ void unit_dot(uint32_t blk, int sub, const UnitAct &a
         lds32xN_any<AL, 3>(blk + 96, sc);
         d = half_bits_to_float(lds16(blk + 108));
 #pragma unroll
+        for (int m = 0; m < 4; ++m) hm[m] >>= 4 * n;   // plane bits j = 0..3 now sit at bit j of every byte
+        int S[4];
+#pragma unroll
         for (int j = 0; j < 4; ++j) {
-            int s = 0;
+            int t = 0;
 #pragma unroll
             for (int m = 0; m < 4; ++m) {
-                const uint32_t q2 = (qs[m] >> (2 * j)) & 0x03030303u;
-                const uint32_t hb = (hm[m] >> (4 * n + j)) & 0x01010101u;
-                s = dp4a_us(q2 | (hb << 2), a.q[4 * j + m], s);
+                // q2 | hbit << 2 in one select: low two bits from qs, bit 2 from hmask
+                const uint32_t hb = (j < 2 ? hm[m] << (2 - j) : hm[m] >> (j - 2)) & 0x04040404u;
+                const uint32_t q = ((qs[m] >> (2 * j)) & 0x03030303u) | hb;
+                t = dp4a_us(q, a.q[4 * j + m], t);
             }
-            s -= 4 * a.bs[j];  // q3 = (q2 | hb<<2) - 4
-            // 6-bit scale k = 8n+2j+h: low nibble from bytes 0..7, high two bits from bytes 8..11
-            const int k = 8 * n + 2 * j + h;
-            const uint32_t lowsrc = (k & 4) ? sc[1] : sc[0];
-            uint32_t lo = (lowsrc >> (8 * (k & 3))) & 0xffu;
-            lo = (k < 8) ? (lo & 0xFu) : (lo >> 4);
-            const uint32_t hi = (sc[2] >> (8 * (k & 3) + 2 * (k >> 2))) & 3u;
-            isum += ((int)(lo | (hi << 4)) - 32) * s;
+            S[j] = t;   // |S| <= 16*7*127: fits 16 bits
         }
+        // q3 = (q2 | hbit << 2) - 4: subtract 4 * bsum of the group
+        const int b01 = a.bs[0], b23 = a.bs[1];
+        S[0] -= 4 * (int)(short)(b01 & 0xffff); S[1] -= 4 * (b01 >> 16);
+        S[2] -= 4 * (int)(short)(b23 & 0xffff); S[3] -= 4 * (b23 >> 16);
+        // 6-bit scales of groups k = 8n + 2j + h: low nibbles in bytes 0..7 (low half for k < 8,
+        // high half for k >= 8), the two high bits in bytes 8..11 at bit 2*(k>>2) of byte k&3
+        const uint32_t lo = (__byte_perm(sc[0], sc[1], h ? 0x7531u : 0x6420u) >> (4 * n)) & 0x0F0F0F0Fu;
+        const uint32_t hs = __byte_perm(sc[2], 0, h ? 0x3131u : 0x2020u) >> (4 * n);
+        const uint32_t hi = (hs & 0x00000303u) | ((hs >> 2) & 0x03030000u);
+        const uint32_t sc6 = lo | (hi << 4);
+        const int tot = S[0] + S[1] + S[2] + S[3];
+        // sum (sc6 - 32) * S; |S| can reach 16*7*127 + 4*16*127 which still fits 16 bits
+        isum = dp2a_hi_su(pack16(S[2], S[3]), sc6, dp2a_lo_su(pack16(S[0], S[1]), sc6, 0)) - 32 * tot;
     } else if (TYPE == Q4_K) {
         // d @0, dmin @2, scales[12] @4, qs[128] @16
         const int c = sub;

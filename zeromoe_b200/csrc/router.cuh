@@ -32,6 +32,8 @@ struct PlanOut {
     int *item_offs_gu; // [E+1]
     int *item_offs_dn; // [E+1]
     int *freq;         // [E] expert histogram (reference scratch.expert_freq), may be null
+    int *aoffs;        // [E] offs[active[a]]
+    int *antok;        // [E] pairs of active[a]
     int nrt_gu, nrt_dn;  // row tiles per expert of the two projections
 };
 
@@ -140,30 +142,56 @@ __device__ void route_token_warp(const RouterSpec &sp, const float *row_in, floa
 }
 
 // CSR of pairs by expert plus the item spaces of the projections.  Called by
-// all threads of ONE CTA; cnt_s/pre_s: shared scratch of E+1 ints each.
+// all threads of ONE CTA; cnt_s/pre_s: shared scratch of E+1 ints each; ids_s:
+// optional shared scratch of P ints (a copy of ids that the stable fill scans).
 // ids: [T*K] (entries outside [0,E) are skipped: negative = inactive route,
 // reference backends/ggml/mmid_route_skip.hpp:60-67).
-__device__ void build_plan_cta(const int32_t *ids, int P, int E, const PlanOut &po, int *cnt_s, int *pre_s) {
-    const int tid = threadIdx.x, nt = blockDim.x;
+__device__ void build_plan_cta(const int32_t *ids, int P, int E, const PlanOut &po, int *cnt_s, int *pre_s,
+                               int *ids_s) {
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
     for (int e = tid; e <= E; e += nt) cnt_s[e] = 0;
     __syncthreads();
     for (int p = tid; p < P; p += nt) {
         const int e = ids[p];
+        if (ids_s) ids_s[p] = e;
         if (e >= 0 && e < E) atomicAdd(&cnt_s[e], 1);
     }
     __syncthreads();
-    if (tid == 0) {
-        int run = 0, na = 0, igu = 0, idn = 0;
-        po.item_offs_gu[0] = 0;
-        po.item_offs_dn[0] = 0;
-        for (int e = 0; e < E; ++e) {
+    if (tid < 32) {
+        // warp scan over contiguous chunks of experts: pairs, active experts, items
+        const int per = (E + 31) / 32, e0 = min(E, lane * per), e1 = min(E, e0 + per);
+        int cs = 0, as = 0, gs = 0, ds = 0;
+        for (int e = e0; e < e1; ++e) {
+            const int c = cnt_s[e];
+            cs += c;
+            if (c > 0) {
+                const int ntc = (c + MMID_MAXTOK - 1) / MMID_MAXTOK;
+                ++as; gs += ntc * po.nrt_gu; ds += ntc * po.nrt_dn;
+            }
+        }
+        int xs[4] = {cs, as, gs, ds}, tot[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            int v = xs[q];
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, v, off);
+                if (lane >= off) v += o;
+            }
+            tot[q] = __shfl_sync(0xffffffffu, v, 31);
+            xs[q] = v - xs[q];  // exclusive
+        }
+        int run = xs[0], na = xs[1], igu = xs[2], idn = xs[3];
+        for (int e = e0; e < e1; ++e) {
             const int c = cnt_s[e];
             pre_s[e] = run;
             po.offs[e] = run;
             if (po.freq) po.freq[e] = c;
             if (c > 0) {
-                po.active[na] = e;
                 const int ntc = (c + MMID_MAXTOK - 1) / MMID_MAXTOK;
+                po.active[na] = e;
+                po.aoffs[na] = run;
+                po.antok[na] = c;
                 igu += ntc * po.nrt_gu;
                 idn += ntc * po.nrt_dn;
                 ++na;
@@ -172,17 +200,22 @@ __device__ void build_plan_cta(const int32_t *ids, int P, int E, const PlanOut &
             }
             run += c;
         }
-        po.offs[E] = run;
-        po.hdr[0] = na; po.hdr[1] = igu; po.hdr[2] = idn; po.hdr[3] = run;
+        if (lane == 0) {
+            po.item_offs_gu[0] = 0;
+            po.item_offs_dn[0] = 0;
+            po.offs[E] = tot[0];
+            po.hdr[0] = tot[1]; po.hdr[1] = tot[2]; po.hdr[2] = tot[3]; po.hdr[3] = tot[0];
+        }
     }
     __syncthreads();
     if (P <= 8192) {
         // stable fill: thread e walks the pairs in order
+        const int *src = ids_s ? ids_s : ids;
         for (int e = tid; e < E; e += nt) {
             if (cnt_s[e] == 0) continue;
             int w = pre_s[e];
             for (int p = 0; p < P; ++p)
-                if (ids[p] == e) po.slot[w++] = p;
+                if (src[p] == e) po.slot[w++] = p;
         }
     } else {
         for (int p = tid; p < P; p += nt) {

@@ -147,6 +147,20 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
     return d;
 }
 
+// dp2a: two signed 16-bit halves of a times two unsigned bytes of b (lo: bytes 0,1; hi: bytes 2,3)
+__device__ __forceinline__ int dp2a_lo_su(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp2a_hi_su(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// low 16 bits of lo and of hi packed into one word
+__device__ __forceinline__ uint32_t pack16(int lo, int hi) { return __byte_perm((uint32_t)lo, (uint32_t)hi, 0x5410); }
+
 __device__ __forceinline__ float half_bits_to_float(uint32_t h) {
     return __half2float(__ushort_as_half((unsigned short)(h & 0xffffu)));
 }

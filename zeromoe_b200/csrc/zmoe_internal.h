@@ -15,6 +15,8 @@ namespace zmoe {
 struct PlanBuffers {
     int *hdr = nullptr, *active = nullptr, *offs = nullptr, *slot = nullptr;
     int *item_offs_gu = nullptr, *item_offs_dn = nullptr, *freq = nullptr;
+    int *aoffs = nullptr, *antok = nullptr;
+    int cap_e = 0;
 };
 
 struct RouterArgs {
