@@ -80,6 +80,22 @@ void launch_glm5next_router_topk(float *logits, const float *bias, int32_t *ids,
                                  int n_experts, int topk, int gating_func, int normalize, float weight_scale,
                                  void *stream);
 
+/* No counterpart in the reference.  y[S,O] = x[S,I] . W[O,I]^T like the launch_*_matmul
+ * symbols above (type = ZMOE_TYPE_*, same results bit for bit), for callers that must not
+ * allocate device memory when they call: engines that gave the whole GPU to their own pool,
+ * code running inside someone else's stream capture, real-time loops.  The quantised
+ * activations and the work plan live in a fixed array inside the library image instead of
+ * cudaMalloc'ed buffers; the call makes no cudaMalloc / cudaFree.
+ *   - Every GPU that loads the library holds ZMOE_NOALLOC_SCRATCH_BYTES for this until exit.
+ *   - Problems needing more (about S * 1.4 * I bytes) return ZMOE_ERR_CAPACITY.
+ *   - The first call on each device looks the array's address up (cudaGetSymbolAddress with
+ *     that device current); make that first call before any stream capture begins.
+ *   - All calls share the array: calls whose kernels may overlap on the GPU race.  Order
+ *     them on one stream or with events.
+ * Returns a ZMOE_* status; work is enqueued on `stream`. */
+#define ZMOE_NOALLOC_SCRATCH_BYTES (1u << 20)
+int zmoe_matmul_noalloc(int type, float *y, const float *x, const void *w, int S, int I, int O, void *stream);
+
 /* grow the per-device scratch of the entry points above to hold `rows`
  * activation rows of `I` elements (allocates; not capturable) */
 int zmoe_reserve(int rows, int I);

@@ -19,7 +19,7 @@ ERRORS = {0: "OK", -1: "ARG", -2: "TYPE", -3: "SHAPE", -4: "ALIGN", -5: "CUDA", 
 EXPORTS = [
     "launch_q2_K_matmul", "launch_q2_K_matmul_stream", "launch_q3_K_matmul", "launch_q3_K_matmul_stream",
     "launch_q4_K_matmul", "launch_iq2_xxs_matmul", "launch_expert_swiglu", "launch_expert_scatter_accum",
-    "launch_expert_scatter_add", "launch_glm5next_router_topk", "zmoe_reserve", "zmoe_last_status",
+    "launch_expert_scatter_add", "launch_glm5next_router_topk", "zmoe_matmul_noalloc", "zmoe_reserve", "zmoe_last_status",
     "zmoe_f32_quant_hook", "zeromoe_install_f32_quant_graph_hook", "zeromoe_f32_quant_graph_launches",
     "zmoe_ctx_create", "zmoe_ctx_destroy", "zmoe_layer_create", "zmoe_layer_destroy", "zmoe_route",
     "zmoe_set_routes", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
@@ -78,6 +78,7 @@ def load():
     L.launch_expert_scatter_add.restype = None
     L.launch_glm5next_router_topk.argtypes = [vp, vp, vp, vp, i, i, i, i, i, f, vp]
     L.launch_glm5next_router_topk.restype = None
+    L.zmoe_matmul_noalloc.argtypes = [i, vp, vp, vp, i, i, i, vp]
     L.zmoe_reserve.argtypes = [i, i]
     L.zmoe_f32_quant_hook.argtypes = [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor),
                                       vp, C.c_bool]
