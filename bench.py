@@ -250,7 +250,8 @@ def main():
     for l in range(LAYERS):
         wg, wu, wd, wr = make_layer_weights(args.seed, l, dev, e_lo, e_hi)
         weights.append((wg, wu, wd, wr))
-        layers.append(lib.Layer(ctx, D, F, n_local, K, TYPES, wg, wu, wd, router_w=wr if world == 1 else None))
+        if world == 1:
+            layers.append(lib.Layer(ctx, D, F, n_local, K, TYPES, wg, wu, wd, router_w=wr))
     xs = make_inputs(args.seed, T, dev, rank)
     outs = [torch.empty((T, D), device=dev) for _ in range(LAYERS)]
     stream = torch.cuda.current_stream()

@@ -187,6 +187,9 @@ int zmoe_moe_forward_host(zmoe_layer *layer, const float *x_host, float *out_hos
 /* copies of the current route table / intermediates to host (synchronise the stream first) */
 int zmoe_get_routes(zmoe_ctx *ctx, int T, int topk, int32_t *ids_host, float *weights_host);
 int zmoe_get_expert_freq(zmoe_ctx *ctx, int n_experts, int32_t *freq_host);
+/* device-to-device copy of the current route table, enqueued on `stream` (for exchanging
+ * routes between expert-parallel ranks without a host round trip) */
+int zmoe_copy_routes(zmoe_ctx *ctx, int T, int topk, int32_t *ids_dev, float *weights_dev, void *stream);
 int zmoe_get_probs(zmoe_ctx *ctx, int T, int n_experts, float *probs_host);
 int zmoe_get_act(zmoe_ctx *ctx, int n_pairs, int d_ff, float *act_host);
 /* reads and clears the device error flag: 0, or ZMOE_ERR_DEVICE_WAIT */

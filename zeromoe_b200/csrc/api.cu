@@ -329,6 +329,15 @@ int zmoe_get_routes(zmoe_ctx *c, int T, int topk, int32_t *ids_host, float *weig
     return rc ? ZMOE_ERR_CUDA : ZMOE_OK;
 }
 
+int zmoe_copy_routes(zmoe_ctx *c, int T, int topk, int32_t *ids_dev, float *weights_dev, void *stream) {
+    if (!c || T <= 0 || topk <= 0 || (size_t)T * topk > (size_t)c->max_t * c->max_k) return ZMOE_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = 0;
+    if (ids_dev) rc |= ok(cudaMemcpyAsync(ids_dev, c->ids, (size_t)T * topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
+    if (weights_dev) rc |= ok(cudaMemcpyAsync(weights_dev, c->weights, (size_t)T * topk * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    return rc ? ZMOE_ERR_CUDA : ZMOE_OK;
+}
+
 int zmoe_get_expert_freq(zmoe_ctx *c, int n_experts, int32_t *freq_host) {
     if (!c || !freq_host || n_experts <= 0 || n_experts > c->max_e) return ZMOE_ERR_ARG;
     return ok(cudaMemcpy(freq_host, c->plan.b.freq, (size_t)n_experts * sizeof(int32_t), cudaMemcpyDeviceToHost));

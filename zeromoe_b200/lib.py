@@ -23,7 +23,7 @@ EXPORTS = [
     "zmoe_f32_quant_hook", "zeromoe_install_f32_quant_graph_hook", "zeromoe_f32_quant_graph_launches",
     "zmoe_ctx_create", "zmoe_ctx_destroy", "zmoe_layer_create", "zmoe_layer_destroy", "zmoe_route",
     "zmoe_set_routes", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
-    "zmoe_get_expert_freq", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_check", "zmoe_kernel_launches",
+    "zmoe_get_expert_freq", "zmoe_copy_routes", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_check", "zmoe_kernel_launches",
     "zmoe_quantize_q8_K", "zmoe_block_isums",
 ]
 
@@ -100,6 +100,7 @@ def load():
     L.zmoe_moe_forward_host.argtypes = [vp, vp, vp, i]
     L.zmoe_get_routes.argtypes = [vp, i, i, vp, vp]
     L.zmoe_get_expert_freq.argtypes = [vp, i, vp]
+    L.zmoe_copy_routes.argtypes = [vp, i, i, vp, vp, vp]
     L.zmoe_get_probs.argtypes = [vp, i, i, vp]
     L.zmoe_get_act.argtypes = [vp, i, i, vp]
     L.zmoe_ctx_check.argtypes = [vp]
@@ -142,6 +143,11 @@ class Context:
         check(load().zmoe_get_routes(self.h, T, K, ids.ctypes.data_as(C.c_void_p), w.ctypes.data_as(C.c_void_p)),
               "zmoe_get_routes")
         return ids, w
+
+    def copy_routes(self, ids_dev, weights_dev, stream=None):
+        T, K = ids_dev.shape
+        check(load().zmoe_copy_routes(self.h, T, K, ptr(ids_dev), ptr(weights_dev), _stream_ptr(stream)),
+              "zmoe_copy_routes")
 
     def expert_freq(self, E):
         f = np.zeros(E, dtype=np.int32)
