@@ -192,6 +192,12 @@ int zmoe_get_expert_freq(zmoe_ctx *ctx, int n_experts, int32_t *freq_host);
 int zmoe_copy_routes(zmoe_ctx *ctx, int T, int topk, int32_t *ids_dev, float *weights_dev, void *stream);
 int zmoe_get_probs(zmoe_ctx *ctx, int T, int n_experts, float *probs_host);
 int zmoe_get_act(zmoe_ctx *ctx, int n_pairs, int d_ff, float *act_host);
+/* which expert-FFN kernels run: 0 = choose by shape (tensor-core grouped GEMM once the call
+ * averages 24 or more pairs per expert, decode kernels below that), 1 = decode kernels,
+ * 2 = tensor-core GEMM whenever the shapes allow (rows per expert a multiple of 128, gate and
+ * up of one type).  The activations passed to zmoe_route / zmoe_set_routes must stay valid
+ * until zmoe_expert_ffn has been enqueued. */
+int zmoe_ctx_set_path(zmoe_ctx *ctx, int path);
 /* reads and clears the device error flag: 0, or ZMOE_ERR_DEVICE_WAIT */
 int zmoe_ctx_check(zmoe_ctx *ctx);
 /* number of kernels this library has launched since load (all entry points) */

@@ -276,6 +276,51 @@ def test_moe_layer_vs_oracle(zlib, oracle, dev, case):
     assert torch.equal(out, out2)
 
 
+PREFILL_CASES = [
+    # D, F, E, K, types, T : shapes where an expert sees tens to hundreds of pairs
+    (2048, 768, 16, 4, (synth.Q4_K, synth.Q4_K, synth.Q4_K), 200),       # configuration 1's types, prefill-shaped
+    (1024, 512, 8, 2, (synth.IQ2_XXS, synth.IQ2_XXS, synth.IQ2_XXS), 333),  # configuration 3's type, ragged pair blocks
+    (1024, 512, 8, 2, (synth.Q2_K, synth.Q2_K, synth.Q3_K), 300),        # configuration 2's types
+    (512, 256, 4, 2, (synth.Q4_K, synth.Q4_K, synth.Q4_K), 40),          # fewer pairs than one MMA tile
+]
+
+
+@pytest.mark.parametrize("case", PREFILL_CASES)
+def test_prefill_tensor_core_path_vs_oracle(zlib, oracle, dev, case):
+    """the tcgen05 grouped GEMM (forced with set_path(2)) against the oracle, and against the
+    decode kernels on the same call; the tiled-GEMM router serves T > 64"""
+    import torch
+    D, F, E, K, types, T = case
+    rng = synth.rng_for(23, D, F, E, T)
+    wg = synth.expert_weights(types[0], E, F, D, rng)
+    wu = synth.expert_weights(types[1], E, F, D, rng)
+    wd = synth.expert_weights(types[2], E, D, F, rng)
+    wr, x, probs, ids_ref, w_ref = routed_inputs(oracle, 23 + D + T, T, D, E, K)
+    ctx = zlib.Context(max(T, 16), D, F, E, K)
+    layer = zlib.Layer(ctx, D, F, E, K, types, to_dev(wg, dev), to_dev(wu, dev), to_dev(wd, dev),
+                       router_w=to_dev(wr, dev))
+    xd = to_dev(x, dev)
+    outs = {}
+    for path in (1, 2):
+        ctx.set_path(path)
+        out = torch.full((T, D), float("nan"), device=dev)
+        layer.forward(xd, out)
+        _sync()
+        ctx.check()
+        outs[path] = out.cpu().numpy()
+    ids, wts = ctx.routes(T, K)
+    assert np.array_equal(ids, ids_ref)
+    assert np.allclose(wts, w_ref, atol=1e-5)
+    ref = oracle.moe_ffn(oracle.make_layer(D, F, E, K, types, wg, wu, wd), x, ids_ref, w_ref)
+    assert rel_to_norm(outs[1], ref) < REL_TO_NORM
+    assert rel_to_norm(outs[2], ref) < REL_TO_NORM          # fp16 operands: ~1e-4 here
+    assert np.isfinite(outs[2]).all()
+    out2 = torch.empty((T, D), device=dev)
+    layer.forward(xd, out2)
+    _sync()
+    assert np.array_equal(out2.cpu().numpy().view(np.uint32), outs[2].view(np.uint32))   # reproducible
+
+
 def test_moe_layer_supplied_routes_with_inactive_ids(zlib, oracle, dev):
     """negative ids are inactive routes: they contribute a zero row"""
     import torch

@@ -75,6 +75,11 @@ struct zmoe_ctx {
     float *act = nullptr;      // [P, F] SwiGLU output
     float *act2 = nullptr;     // [2, P, F] gate / up when their types differ (lazy)
     uint8_t *q8act = nullptr;  // packed Q8_K rows of act
+    void *xq_f16 = nullptr;   // [P, D] fp16: layer input rows in expert order after the Q8_K round trip
+    void *actq_f16 = nullptr; // [P, F] fp16: act after the Q8_K round trip (tensor-core path)
+    float *xscale = nullptr, *actscale = nullptr;  // per-row powers of two of the fp16 copies
+    const float *x_last = nullptr;  // the activations the current route table was built from
+    int path = 0;              // 0 auto, 1 decode kernels, 2 tensor-core GEMM
     float *ydown = nullptr;    // [P, D] per-pair down-projection output
     float *logits = nullptr;   // [T, E] router logits, then probabilities
     int32_t *ids = nullptr;    // [T, K]
@@ -113,6 +118,10 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     rc |= dev_alloc(&c->q8x2, (size_t)max_tokens * q8row_stride(max_d_model));
     rc |= dev_alloc(&c->act, P * max_d_ff);
     rc |= dev_alloc(&c->q8act, P * q8row_stride(max_d_ff));
+    rc |= dev_alloc(reinterpret_cast<uint16_t **>(&c->xq_f16), P * max_d_model);
+    rc |= dev_alloc(reinterpret_cast<uint16_t **>(&c->actq_f16), P * max_d_ff);
+    rc |= dev_alloc(&c->xscale, P);
+    rc |= dev_alloc(&c->actscale, P);
     rc |= dev_alloc(&c->ydown, P * max_d_model);
     rc |= dev_alloc(&c->logits, (size_t)max_tokens * max_experts);
     rc |= dev_alloc(&c->ids, P);
@@ -138,6 +147,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
 
 void zmoe_ctx_destroy(zmoe_ctx *c) {
     if (!c) return;
+    cudaFree(c->xq_f16); cudaFree(c->actq_f16); cudaFree(c->xscale); cudaFree(c->actscale);
     cudaFree(c->q8x); cudaFree(c->q8x2); cudaFree(c->act); cudaFree(c->act2); cudaFree(c->q8act); cudaFree(c->ydown);
     cudaFree(c->logits); cudaFree(c->ids); cudaFree(c->weights); cudaFree(c->err); cudaFree(c->ticket);
     cudaFree(c->x_stage); cudaFree(c->out_stage);
@@ -207,14 +217,18 @@ int zmoe_route(zmoe_layer *L, const float *x_dev, int T, void *stream) {
     a.plan = c->plan.b;
     a.nrt_gu = L->nrt_gu; a.nrt_dn = L->nrt_dn;
     a.ticket = c->ticket;
-    int rc = launch_router_decode(a, static_cast<cudaStream_t>(stream));
-    g_launches += 1;
+    // one CTA per (expert, 4 tokens) re-reads every activation row E times: fine for decode
+    // batches, replaced by a tiled GEMM beyond 64 tokens
+    const bool big = T > 64;
+    int rc = big ? launch_router_prefill(a, static_cast<cudaStream_t>(stream))
+                 : launch_router_decode(a, static_cast<cudaStream_t>(stream));
+    g_launches += big ? 4 : 1;
     if (!rc && q8_layout_of(L->d.up.type) != a.q8_layout) {
         rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x2, T, L->d.d_model, q8_layout_of(L->d.up.type),
                                   static_cast<cudaStream_t>(stream));
         g_launches += 1;
     }
-    if (!rc) c->routed_t = T;
+    if (!rc) { c->routed_t = T; c->x_last = x_dev; }
     return rc;
 }
 
@@ -233,7 +247,7 @@ int zmoe_set_routes(zmoe_layer *L, const float *x_dev, const int32_t *ids_dev, c
         g_launches += 1;
     }
     if (!rc) rc = launch_plan_from_ids(c->ids, (int)P, L->d.n_experts, c->plan.b, L->nrt_gu, L->nrt_dn, st);
-    if (!rc) { g_launches += 2; c->routed_t = T; }
+    if (!rc) { g_launches += 2; c->routed_t = T; c->x_last = x_dev; }
     return rc;
 }
 
@@ -256,6 +270,36 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
     m.clamp = d.swiglu_clamp;
     m.clamp_fused = d.swiglu_clamp_fused;
     int rc;
+    // many pairs per expert: the contraction is compute-bound and goes to the tensor cores
+    const bool gemm_ok = L->dual && c->x_last && gemm_sm100_supported(d.gate.type, d.d_model, d.d_ff) &&
+                         gemm_sm100_supported(d.down.type, d.d_ff, d.d_model) && d.n_experts <= 512;
+    const bool use_gemm = gemm_ok && (c->path == 2 || (c->path == 0 && (long)P >= 24L * d.n_experts));
+    if (use_gemm) {
+        if (ev_before) cudaEventRecord(static_cast<cudaEvent_t>(ev_before), st);
+        GemmLaunch g;
+        g.plan = c->plan.b; g.err = c->err; g.n_sm = c->n_sm;
+        g.clamp = d.swiglu_clamp; g.clamp_fused = d.swiglu_clamp_fused;
+        rc = launch_q8_roundtrip_f16(c->x_last, d.d_model, c->xq_f16, c->xscale, c->plan.b, P, d.topk, d.d_model, st);
+        g.type = d.gate.type; g.dual = true;
+        g.w0 = d.gate.data_dev; g.w1 = d.up.data_dev;
+        g.stride0 = d.gate.expert_stride; g.stride1 = d.up.expert_stride;
+        g.I = d.d_model; g.O = d.d_ff;
+        g.x_f16 = c->xq_f16; g.xscale = c->xscale; g.x_rows = c->max_t * c->max_k;
+        g.y = c->act; g.ldy = d.d_ff;
+        if (!rc) rc = launch_gemm_sm100(g, st);
+        if (ev_after) cudaEventRecord(static_cast<cudaEvent_t>(ev_after), st);
+        if (!rc) rc = launch_q8_roundtrip_f16(c->act, d.d_ff, c->actq_f16, c->actscale, c->plan.b, P, 1, d.d_ff, st);
+        g.type = d.down.type; g.dual = false;
+        g.w0 = d.down.data_dev; g.w1 = nullptr;
+        g.stride0 = d.down.expert_stride; g.stride1 = 0;
+        g.I = d.d_ff; g.O = d.d_model;
+        g.x_f16 = c->actq_f16; g.xscale = c->actscale; g.x_rows = c->max_t * c->max_k;
+        g.y = c->ydown; g.ldy = d.d_model;
+        if (!rc) rc = launch_gemm_sm100(g, st);
+        if (!rc) rc = launch_combine(out_dev, c->ydown, c->weights, c->ids, T, d.topk, d.d_model, d.n_experts, accumulate, st);
+        g_launches += 5;
+        return rc;
+    }
     if (ev_before) cudaEventRecord(static_cast<cudaEvent_t>(ev_before), st);
     if (L->dual) {
         m.type = d.gate.type; m.dual = true;
@@ -351,6 +395,12 @@ int zmoe_get_probs(zmoe_ctx *c, int T, int n_experts, float *probs_host) {
 int zmoe_get_act(zmoe_ctx *c, int n_pairs, int d_ff, float *act_host) {
     if (!c || !act_host || n_pairs <= 0 || (size_t)n_pairs * d_ff > (size_t)c->max_t * c->max_k * c->max_f) return ZMOE_ERR_ARG;
     return ok(cudaMemcpy(act_host, c->act, (size_t)n_pairs * d_ff * sizeof(float), cudaMemcpyDeviceToHost));
+}
+
+int zmoe_ctx_set_path(zmoe_ctx *c, int path) {
+    if (!c || path < 0 || path > 2) return ZMOE_ERR_ARG;
+    c->path = path;
+    return ZMOE_OK;
 }
 
 int zmoe_ctx_check(zmoe_ctx *c) {

@@ -119,6 +119,76 @@ int launch_router_decode(const RouterArgs &a, cudaStream_t st) {
 }
 
 // ------------------------------------------------------------------------
+// prefill-shaped router: logits[T, E] = x[T, D] . wr[E, D]^T as a tiled f32 GEMM (64 x 64 tile,
+// 4 x 4 per thread), then one warp per token for gating / top-k, then the stand-alone planner.
+// Replaces the per-token dense_proj + partial_sort loop of reference
+// core/moe_router_service.cpp:1202-1214,1409-1474 for batches where one CTA per
+// (expert, 4 tokens) would re-read the activations too often.
+// ------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) router_logits_gemm_kernel(const float *__restrict__ x,
+                                                                 const float *__restrict__ wr,
+                                                                 float *__restrict__ logits, int T, int D, int E) {
+    __shared__ float xs[16][64 + 4], ws[16][64 + 4];
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x;
+    const int t0 = blockIdx.y * 64, e0 = blockIdx.x * 64;
+    const int lr = tid >> 2, lc = (tid & 3) * 4;       // loader: row 0..63, k offset 0,4,8,12
+    const int tm = (tid >> 4) * 4, tn = (tid & 15) * 4;  // compute: 4 tokens x 4 experts
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < D; k0 += 16) {
+        float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), wv = xv;
+        if (t0 + lr < T) xv = *reinterpret_cast<const float4 *>(x + (size_t)(t0 + lr) * D + k0 + lc);
+        if (e0 + lr < E) wv = *reinterpret_cast<const float4 *>(wr + (size_t)(e0 + lr) * D + k0 + lc);
+        __syncthreads();
+        xs[lc + 0][lr] = xv.x; xs[lc + 1][lr] = xv.y; xs[lc + 2][lr] = xv.z; xs[lc + 3][lr] = xv.w;
+        ws[lc + 0][lr] = wv.x; ws[lc + 1][lr] = wv.y; ws[lc + 2][lr] = wv.z; ws[lc + 3][lr] = wv.w;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float4 a = *reinterpret_cast<const float4 *>(&xs[k][tm]);
+            const float4 b = *reinterpret_cast<const float4 *>(&ws[k][tn]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (t0 + tm + i < T && e0 + tn + j < E) logits[(size_t)(t0 + tm + i) * E + e0 + tn + j] = acc[i][j];
+}
+
+__global__ void __launch_bounds__(128) router_select_kernel(float *logits, const float *bias, int32_t *ids,
+                                                            float *weights, int T, RouterSpec sp) {
+    extern __shared__ float rsel[];
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    float *prob_s = rsel + (size_t)warp * 2 * sp.E;
+    route_token_warp(sp, logits + (size_t)t * sp.E, logits + (size_t)t * sp.E, bias, ids + (size_t)t * sp.K,
+                     weights + (size_t)t * sp.K, prob_s, prob_s + sp.E, lane);
+}
+
+int launch_router_prefill(const RouterArgs &a, cudaStream_t st) {
+    if (a.D % 16 || (size_t)8 * a.E * sizeof(float) > 48 * 1024) return ZMOE_ERR_SHAPE;
+    int rc = launch_pdl(router_logits_gemm_kernel, dim3((a.E + 63) / 64, (a.T + 63) / 64), dim3(256), 0, st, a.x, a.wr,
+                        a.logits, a.T, a.D, a.E) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+    RouterSpec sp{a.E, a.K, a.gating, a.normalize, a.weight_scale, a.n_groups, a.n_groups_used};
+    if (!rc)
+        rc = launch_pdl(router_select_kernel, dim3((a.T + 3) / 4), dim3(128), (size_t)8 * a.E * sizeof(float), st,
+                        a.logits, a.bias, a.ids, a.weights, a.T, sp) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+    if (!rc) rc = launch_quantize_rows(a.x, a.D, a.q8x, a.T, a.D, a.q8_layout, st);
+    if (!rc) rc = launch_plan_from_ids(a.ids, a.T * a.K, a.E, a.plan, a.nrt_gu, a.nrt_dn, st);
+    return rc;
+}
+
+// ------------------------------------------------------------------------
 // stand-alone planners
 // ------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) plan_from_ids_kernel(const int32_t *ids, int P, int E, PlanOut po) {

@@ -85,6 +85,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// The same for warps that expect to wait long while other warps of the SM do the work: sleep
+// between polls so the polling does not take issue slots from them.
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t *bar, uint32_t parity, uint32_t sleep_ns,
+                                                uint32_t limit = (1u << 22)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(sleep_ns);
+    }
+    return false;
+}
 
 // 1-D bulk asynchronous copy global -> shared of this CTA, completion counted
 // in bytes on `bar`.  Source, destination and size must be multiples of 16.

@@ -65,7 +65,31 @@ struct MmidLaunch {
 };
 int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st);
 
+// prefill path: tcgen05 grouped GEMM over fp16 activations (Q8_K round trip applied, rows scaled)
+struct GemmLaunch {
+    int type;
+    bool dual;
+    const void *w0, *w1;
+    size_t stride0, stride1;
+    int I, O;
+    const void *x_f16;     // sorted activation rows [x_rows, I] fp16
+    const float *xscale;   // their per-row scales
+    int x_rows;            // rows the buffer holds
+    float *y;
+    int ldy;
+    PlanBuffers plan;
+    float clamp;
+    int clamp_fused;
+    int *err;
+    int n_sm;
+};
+bool gemm_sm100_supported(int type, int I, int O);
+int launch_gemm_sm100(const GemmLaunch &L, cudaStream_t st);
+int launch_q8_roundtrip_f16(const float *x, int ldx, void *out_f16, float *scale, const PlanBuffers &plan,
+                            int max_rows, int xdiv, int I, cudaStream_t st);
+
 int launch_router_decode(const RouterArgs &a, cudaStream_t st);
+int launch_router_prefill(const RouterArgs &a, cudaStream_t st);  // four launches; for large T
 int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
                          cudaStream_t st);
 int launch_plan_dense(int S, const PlanBuffers &plan, int nrt, cudaStream_t st);

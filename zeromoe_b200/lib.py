@@ -23,7 +23,7 @@ EXPORTS = [
     "zmoe_f32_quant_hook", "zeromoe_install_f32_quant_graph_hook", "zeromoe_f32_quant_graph_launches",
     "zmoe_ctx_create", "zmoe_ctx_destroy", "zmoe_layer_create", "zmoe_layer_destroy", "zmoe_route",
     "zmoe_set_routes", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
-    "zmoe_get_expert_freq", "zmoe_copy_routes", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_check", "zmoe_kernel_launches",
+    "zmoe_get_expert_freq", "zmoe_copy_routes", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_set_path", "zmoe_ctx_check", "zmoe_kernel_launches",
     "zmoe_quantize_q8_K", "zmoe_block_isums",
 ]
 
@@ -104,6 +104,7 @@ def load():
     L.zmoe_get_probs.argtypes = [vp, i, i, vp]
     L.zmoe_get_act.argtypes = [vp, i, i, vp]
     L.zmoe_ctx_check.argtypes = [vp]
+    L.zmoe_ctx_set_path.argtypes = [vp, i]
     L.zmoe_quantize_q8_K.argtypes = [vp, vp, i, i, i, vp]
     L.zmoe_block_isums.argtypes = [i, vp, vp, vp, vp, i, i, vp]
     _lib = L
@@ -136,6 +137,10 @@ class Context:
 
     def check(self):
         check(load().zmoe_ctx_check(self.h), "zmoe_ctx_check")
+
+    def set_path(self, path):
+        """0 auto, 1 decode kernels, 2 tensor-core GEMM"""
+        check(load().zmoe_ctx_set_path(self.h, path), "zmoe_ctx_set_path")
 
     def routes(self, T, K):
         ids = np.zeros((T, K), dtype=np.int32)
