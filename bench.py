@@ -41,8 +41,9 @@ RB_GU = D // 256 * 84      # bytes per gate / up row
 RB_DN = F // 256 * 110     # bytes per down row
 METRIC = "moe_layer_stack_decode_tokens_per_s"
 UNIT = "tokens/s"
-HALF_OFFS = {Q2_K: (80, 82), Q3_K: (108,)}
-BB = {Q2_K: 84, Q3_K: 110}
+IQ2_XXS = 16
+HALF_OFFS = {Q2_K: (80, 82), Q3_K: (108,), IQ2_XXS: (0,)}
+BB = {Q2_K: 84, Q3_K: 110, IQ2_XXS: 66}
 
 
 def workload_name(T):
@@ -96,6 +97,51 @@ def make_inputs(seed, T, device, rank=0):
     gen = torch.Generator(device=device)
     gen.manual_seed(seed * 31 + 17 + 1000 * rank)
     return [torch.randn((T, D), device=device, generator=gen) for _ in range(LAYERS)]
+
+
+def prefill_probe(lib, dev, seed, peaks, reps=5):
+    """Prefill-shaped call of the third benchmark configuration: hidden 4096, 128 experts, top-8,
+    ffn 1536, IQ2_XXS weights, 4096 tokens, expert load skewed Zipf(s=1.1).  One layer, router
+    included; reports tokens/s and tensor-core throughput of the whole call."""
+    import torch
+    T = 4096
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed * 13 + 5)
+    nbD, nbF = D // 256, F // 256
+    wg = torch_blocks(IQ2_XXS, E * F * nbD, gen, dev).reshape(E, F, nbD * 66)
+    wu = torch_blocks(IQ2_XXS, E * F * nbD, gen, dev).reshape(E, F, nbD * 66)
+    wd = torch_blocks(IQ2_XXS, E * D * nbF, gen, dev).reshape(E, D, nbF * 66)
+    wr = torch.randn((E, D), device=dev, generator=gen) * 0.02
+    # Zipf(1.1) over a random expert ranking, as a selection bias on the router probabilities
+    rank = torch.randperm(E, device=dev, generator=gen).double() + 1.0
+    pz = rank.pow(-1.1)
+    bias = (2.0 * pz / pz.sum()).float()
+    x = torch.randn((T, D), device=dev, generator=gen)
+    ctx = lib.Context(T, D, F, E, K)
+    layer = lib.Layer(ctx, D, F, E, K, (IQ2_XXS,) * 3, wg, wu, wd, router_w=wr, router_bias=bias)
+    out = torch.empty((T, D), device=dev)
+    for _ in range(3):
+        layer.forward(x, out)
+    torch.cuda.synchronize()
+    ctx.check()
+    freq = ctx.expert_freq(E)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        layer.forward(x, out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    flops = T * K * 3 * 2 * D * F
+    tf = flops / (ms * 1e-3) / 1e12
+    res = {"workload": "prefill grouped GEMM: hidden 4096, 128 experts top-8, ffn 1536, IQ2_XXS, 4096 tokens, "
+                       "Zipf(1.1) expert load", "tokens_per_s": T / (ms * 1e-3), "ms_per_call": ms,
+           "tflops": tf, "bound": "tensor", "peak_tflops": peaks["bf16_tflops"], "frac": tf / peaks["bf16_tflops"],
+           "pairs_per_expert": {"max": int(freq.max()), "median": float(np.median(freq)), "min": int(freq.min())},
+           "kernel": "gemm_sm100_kernel (tcgen05.mma kind::f16, fp16 operands, f32 TMEM accumulators)"}
+    del layer, ctx, wg, wu, wd
+    torch.cuda.empty_cache()
+    return res
 
 
 # ---------------------------------------------------------------------------
@@ -217,6 +263,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra batch sizes of the sweep")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill-shaped probe")
     ap.add_argument("--layers", type=int, default=8, help="layers in the stack (8 = the benchmark configuration; "
                     "fewer only for profiler captures)")
     args = ap.parse_args()
@@ -345,6 +392,33 @@ def main():
                "api": "zmoe_moe_forward_host per layer (pinned host in, host out, stream sync per layer)"}
         assert torch.equal(oh[0], outs[0].cpu()), "host entry and device entry disagree"
 
+    else:
+        # expert parallel: every rank copies its own tokens in and its own output rows out
+        xh = [x.cpu().pin_memory() for x in xs]
+        oh = [torch.empty((T, D), dtype=torch.float32).pin_memory() for _ in range(LAYERS)]
+        xdev = [torch.empty_like(x) for x in xs]
+
+        def step_host():
+            for l in range(LAYERS):
+                xdev[l].copy_(xh[l], non_blocking=True)
+                shard.forward(l, xdev[l], outs[l])
+                oh[l].copy_(outs[l], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+        for _ in range(3):
+            step_host()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_host()
+        barrier()
+        dt = (time.perf_counter() - t0) / args.steps
+        tt = torch.tensor([dt], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item())
+        e2e = {"value": t_all / dt, "unit": UNIT, "h2d_bytes_per_step": LAYERS * T * D * 4 * world,
+               "d2h_bytes_per_step": LAYERS * T * D * 4 * world, "ms_per_step": dt * 1e3,
+               "api": "ExpertShard.forward per layer with pinned host activations in and host output back"}
+
     # ---- roofline of the dominant kernel (gate/up matmul + SwiGLU) ---------------------
     roofline, layer_roofline = None, None
     if world == 1 and rank == 0:
@@ -403,6 +477,11 @@ def main():
             ms2 = timed(fn2, args.steps)
             sweep[str(t2)] = {"tokens_per_s": t2 / (ms2 * 1e-3), "ms_per_step": ms2}
 
+    # ---- prefill-shaped probe (tensor-core path) ------------------------------------------
+    prefill = None
+    if world == 1 and rank == 0 and not args.no_prefill and LAYERS == 8:
+        prefill = prefill_probe(lib, dev, args.seed, measured_peaks()[0])
+
     # ---- CPU baseline on a bounded sample -----------------------------------------------
     cpu = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
@@ -432,7 +511,7 @@ def main():
                            "l2": "inputs larger than L2: 7.0 GB of expert weights cycle every step",
                            "launch": "cuda graph replay" if graph is not None else "eager"},
                 "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "roofline": roofline,
-                "layer_stack_roofline": layer_roofline, "sweep": sweep, "cpu_baseline": cpu}
+                "layer_stack_roofline": layer_roofline, "sweep": sweep, "prefill": prefill, "cpu_baseline": cpu}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
