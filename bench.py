@@ -99,12 +99,11 @@ def make_inputs(seed, T, device, rank=0):
     return [torch.randn((T, D), device=device, generator=gen) for _ in range(LAYERS)]
 
 
-def prefill_probe(lib, dev, seed, peaks, reps=5):
+def prefill_probe(lib, dev, seed, peaks, reps=5, E=E, T=4096):
     """Prefill-shaped call of the third benchmark configuration: hidden 4096, 128 experts, top-8,
     ffn 1536, IQ2_XXS weights, 4096 tokens, expert load skewed Zipf(s=1.1).  One layer, router
     included; reports tokens/s and tensor-core throughput of the whole call."""
     import torch
-    T = 4096
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed * 13 + 5)
     nbD, nbF = D // 256, F // 256
@@ -134,8 +133,8 @@ def prefill_probe(lib, dev, seed, peaks, reps=5):
     ms = e0.elapsed_time(e1) / reps
     flops = T * K * 3 * 2 * D * F
     tf = flops / (ms * 1e-3) / 1e12
-    res = {"workload": "prefill grouped GEMM: hidden 4096, 128 experts top-8, ffn 1536, IQ2_XXS, 4096 tokens, "
-                       "Zipf(1.1) expert load", "tokens_per_s": T / (ms * 1e-3), "ms_per_call": ms,
+    res = {"workload": "prefill grouped GEMM: hidden 4096, %d experts top-8, ffn 1536, IQ2_XXS, %d tokens, "
+                       "Zipf(1.1) expert load" % (E, T), "tokens_per_s": T / (ms * 1e-3), "ms_per_call": ms,
            "tflops": tf, "bound": "tensor", "peak_tflops": peaks["bf16_tflops"], "frac": tf / peaks["bf16_tflops"],
            "pairs_per_expert": {"max": int(freq.max()), "median": float(np.median(freq)), "min": int(freq.min())},
            "kernel": "gemm_sm100_kernel (tcgen05.mma kind::f16, fp16 operands, f32 TMEM accumulators)"}
@@ -264,6 +263,9 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra batch sizes of the sweep")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill-shaped probe")
+    ap.add_argument("--prefill-only", action="store_true", help="run only the prefill-shaped probe (profiler captures)")
+    ap.add_argument("--prefill-experts", type=int, default=E)
+    ap.add_argument("--prefill-tokens", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=8, help="layers in the stack (8 = the benchmark configuration; "
                     "fewer only for profiler captures)")
     args = ap.parse_args()
@@ -288,6 +290,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     lib.load()
 
+    if args.prefill_only:
+        print(json.dumps({"prefill": prefill_probe(lib, dev, args.seed, measured_peaks()[0], reps=3,
+                                                   E=args.prefill_experts, T=args.prefill_tokens)}))
+        return
     T = args.tokens
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
     n_local = e_hi - e_lo
