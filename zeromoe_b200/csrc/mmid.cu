@@ -21,7 +21,8 @@ int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
         g->lpr = 32;
         g->upl = (U + 31) / 32;
     }
-    g->ncw = g->upl <= 2 ? 16 : g->upl == 3 ? 12 : 8;
+    // must match the instantiations in pick(): consumer warps per (lanes per row, units per lane)
+    g->ncw = g->lpr == 16 ? 12 : g->upl <= 2 ? 16 : g->upl == 3 ? 12 : 8;
     const int rb = (I / QK_K) * bb;
     const int rpw = 32 / g->lpr;
     int unit = rpw * g->ncw;  // rows of one full pass of the consumer warps
@@ -60,6 +61,11 @@ static KernelFn pick(int lpr, int upl) {
         case 2: return mmid_kernel<TYPE, 8, 2, DUAL, 16>;
         case 3: return mmid_kernel<TYPE, 8, 3, DUAL, 12>;
         case 4: return mmid_kernel<TYPE, 8, 4, DUAL, 8>;
+        }
+    } else if (lpr == 16) {
+        switch (upl) {
+        case 3: return mmid_kernel<TYPE, 16, 3, DUAL, 12>;
+        case 4: return mmid_kernel<TYPE, 16, 4, DUAL, 12>;
         }
     } else {
         switch (upl) {

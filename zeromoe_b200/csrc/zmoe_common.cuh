@@ -80,7 +80,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 // Bounded wait: gives up after `limit` polls and reports failure instead of
 // spinning forever; callers raise an error flag and unwind.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 19)) {
     for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
@@ -88,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32
 // The same for warps that expect to wait long while other warps of the SM do the work: sleep
 // between polls so the polling does not take issue slots from them.
 __device__ __forceinline__ bool mbar_wait_sleep(uint64_t *bar, uint32_t parity, uint32_t sleep_ns,
-                                                uint32_t limit = (1u << 22)) {
+                                                uint32_t limit = (1u << 17)) {
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         __nanosleep(sleep_ns);
