@@ -179,6 +179,12 @@ int zmoe_expert_ffn(zmoe_layer *layer, float *out_dev, int T, int accumulate, vo
  * `stream`, one before and one after the gate/up matmul, for per-kernel timing */
 int zmoe_expert_ffn_events(zmoe_layer *layer, float *out_dev, int T, int accumulate, void *stream,
                            void *ev_before_gate_up, void *ev_after_gate_up);
+/* Dense SwiGLU FFN applied to every token -- the shared expert of reference
+ * backends/ggml/ggml_moe_graph_builder.cpp:94-129 (build_shared_topology).  `layer` must have been
+ * created with n_experts = 1 and topk = 1 over the shared expert's gate / up / down tensors; with
+ * accumulate = 1 the result is added to out_dev (the routed sum).  Overwrites the context's route
+ * table. */
+int zmoe_dense_ffn(zmoe_layer *layer, const float *x_dev, float *out_dev, int T, int accumulate, void *stream);
 /* zmoe_route followed by zmoe_expert_ffn */
 int zmoe_moe_forward(zmoe_layer *layer, const float *x_dev, float *out_dev, int T, void *stream);
 /* the same with host buffers: copies x in, runs the layer, copies out back, synchronises */

@@ -356,6 +356,44 @@ def test_moe_layer_supplied_routes_with_inactive_ids(zlib, oracle, dev):
     assert rel_to_norm(base.cpu().numpy(), ref + 1.0) < REL_TO_NORM
 
 
+def test_deepseek_shaped_layer_with_shared_expert(zlib, oracle, dev):
+    """fourth benchmark configuration, scaled down in expert count only: hidden 7168, ffn 2048,
+    sigmoid gating, 8 groups with the top 4 kept, top-8, normalised weights, Q4_K, one shared expert"""
+    import torch
+    D, F, E, K, T = 7168, 2048, 64, 8, 3
+    types = (synth.Q4_K,) * 3
+    rng = synth.rng_for(29, 0)
+    wg = synth.expert_weights(types[0], E, F, D, rng)
+    wu = synth.expert_weights(types[1], E, F, D, rng)
+    wd = synth.expert_weights(types[2], E, D, F, rng)
+    sg = synth.expert_weights(types[0], 1, F, D, rng)
+    su = synth.expert_weights(types[1], 1, F, D, rng)
+    sd = synth.expert_weights(types[2], 1, D, F, rng)
+    bias = (rng.standard_normal(E) * 0.02).astype(np.float32)
+    wr, x, probs, ids_ref, w_ref = routed_inputs(oracle, 29, T, D, E, K, gating=1, normalize=1, weight_scale=2.5,
+                                                 bias=bias, n_groups=8, n_groups_used=4)
+    ctx = zlib.Context(16, D, F, E, K)
+    routed = zlib.Layer(ctx, D, F, E, K, types, to_dev(wg, dev), to_dev(wu, dev), to_dev(wd, dev),
+                        router_w=to_dev(wr, dev), router_bias=to_dev(bias, dev), gating=1, weights_norm=1,
+                        weights_scale=2.5, n_groups=8, n_groups_used=4)
+    shared = zlib.Layer(ctx, D, F, 1, 1, types, to_dev(sg, dev), to_dev(su, dev), to_dev(sd, dev))
+    xd = to_dev(x, dev)
+    out = torch.empty((T, D), device=dev)
+    routed.forward(xd, out)
+    _sync()
+    ids, wts = ctx.routes(T, K)
+    assert np.array_equal(ids, ids_ref)
+    # every token stays inside its 4 kept groups
+    assert all(len({int(e) // (E // 8) for e in row}) <= 4 for row in ids)
+    shared.dense_ffn(xd, out, accumulate=1)
+    _sync()
+    ctx.check()
+    ref = oracle.moe_ffn(oracle.make_layer(D, F, E, K, types, wg, wu, wd), x, ids_ref, w_ref)
+    ref += oracle.moe_ffn(oracle.make_layer(D, F, 1, 1, types, sg, su, sd), x, np.zeros((T, 1), np.int32),
+                          np.ones((T, 1), np.float32))
+    assert rel_to_norm(out.cpu().numpy(), ref) < REL_TO_NORM
+
+
 def test_moe_forward_host_buffers(zlib, oracle, dev):
     import torch
     D, F, E, K, T = 1024, 512, 16, 4, 4

@@ -78,6 +78,8 @@ struct zmoe_ctx {
     void *xq_f16 = nullptr;   // [P, D] fp16: layer input rows in expert order after the Q8_K round trip
     void *actq_f16 = nullptr; // [P, F] fp16: act after the Q8_K round trip (tensor-core path)
     float *xscale = nullptr, *actscale = nullptr;  // per-row powers of two of the fp16 copies
+    int32_t *zero_ids = nullptr;   // [T] zeros / ones: routes of a dense (single-expert) FFN
+    float *one_w = nullptr;
     const float *x_last = nullptr;  // the activations the current route table was built from
     int path = 0;              // 0 auto, 1 decode kernels, 2 tensor-core GEMM
     float *ydown = nullptr;    // [P, D] per-pair down-projection output
@@ -121,6 +123,8 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     rc |= dev_alloc(reinterpret_cast<uint16_t **>(&c->xq_f16), P * max_d_model);
     rc |= dev_alloc(reinterpret_cast<uint16_t **>(&c->actq_f16), P * max_d_ff);
     rc |= dev_alloc(&c->xscale, P);
+    rc |= dev_alloc(&c->zero_ids, (size_t)max_tokens);
+    rc |= dev_alloc(&c->one_w, (size_t)max_tokens);
     rc |= dev_alloc(&c->actscale, P);
     rc |= dev_alloc(&c->ydown, P * max_d_model);
     rc |= dev_alloc(&c->logits, (size_t)max_tokens * max_experts);
@@ -136,6 +140,17 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
         rc |= ok(cudaMemset(c->err, 0, sizeof(int)));
         rc |= ok(cudaMemset(c->ticket, 0, sizeof(unsigned)));
         rc |= ok(cudaMemset(c->plan.b.hdr, 0, 4 * sizeof(int)));
+        rc |= ok(cudaMemset(c->zero_ids, 0, (size_t)max_tokens * sizeof(int32_t)));
+        // 1.0f = 0x3f800000: fill through a host staging vector (done once)
+        {
+            float *ones = new (std::nothrow) float[max_tokens];
+            if (!ones) rc |= ZMOE_ERR_ARG;
+            else {
+                for (int i = 0; i < max_tokens; ++i) ones[i] = 1.0f;
+                rc |= ok(cudaMemcpy(c->one_w, ones, (size_t)max_tokens * sizeof(float), cudaMemcpyHostToDevice));
+                delete[] ones;
+            }
+        }
     }
     if (rc) {
         zmoe_ctx_destroy(c);
@@ -147,6 +162,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
 
 void zmoe_ctx_destroy(zmoe_ctx *c) {
     if (!c) return;
+    cudaFree(c->zero_ids); cudaFree(c->one_w);
     cudaFree(c->xq_f16); cudaFree(c->actq_f16); cudaFree(c->xscale); cudaFree(c->actscale);
     cudaFree(c->q8x); cudaFree(c->q8x2); cudaFree(c->act); cudaFree(c->act2); cudaFree(c->q8act); cudaFree(c->ydown);
     cudaFree(c->logits); cudaFree(c->ids); cudaFree(c->weights); cudaFree(c->err); cudaFree(c->ticket);
@@ -343,6 +359,15 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
     }
     if (!rc) rc = launch_combine(out_dev, c->ydown, c->weights, c->ids, T, d.topk, d.d_model, d.n_experts, accumulate, st);
     g_launches += 3;
+    return rc;
+}
+
+int zmoe_dense_ffn(zmoe_layer *L, const float *x_dev, float *out_dev, int T, int accumulate, void *stream) {
+    if (!L || !x_dev || !out_dev || T <= 0) return ZMOE_ERR_ARG;
+    if (L->d.n_experts != 1 || L->d.topk != 1) return ZMOE_ERR_STATE;
+    if (T > L->ctx->max_t) return ZMOE_ERR_CAPACITY;
+    int rc = zmoe_set_routes(L, x_dev, L->ctx->zero_ids, L->ctx->one_w, T, stream);
+    if (!rc) rc = zmoe_expert_ffn(L, out_dev, T, accumulate, stream);
     return rc;
 }
 

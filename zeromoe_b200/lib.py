@@ -22,7 +22,7 @@ EXPORTS = [
     "launch_expert_scatter_add", "launch_glm5next_router_topk", "zmoe_matmul_noalloc", "zmoe_reserve", "zmoe_last_status",
     "zmoe_f32_quant_hook", "zeromoe_install_f32_quant_graph_hook", "zeromoe_f32_quant_graph_launches",
     "zmoe_ctx_create", "zmoe_ctx_destroy", "zmoe_layer_create", "zmoe_layer_destroy", "zmoe_route",
-    "zmoe_set_routes", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
+    "zmoe_set_routes", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_dense_ffn", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
     "zmoe_get_expert_freq", "zmoe_copy_routes", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_set_path", "zmoe_ctx_check", "zmoe_kernel_launches",
     "zmoe_quantize_q8_K", "zmoe_block_isums",
 ]
@@ -96,6 +96,7 @@ def load():
     L.zmoe_set_routes.argtypes = [vp, vp, vp, vp, i, vp]
     L.zmoe_expert_ffn.argtypes = [vp, vp, i, i, vp]
     L.zmoe_expert_ffn_events.argtypes = [vp, vp, i, i, vp, vp, vp]
+    L.zmoe_dense_ffn.argtypes = [vp, vp, vp, i, i, vp]
     L.zmoe_moe_forward.argtypes = [vp, vp, vp, i, vp]
     L.zmoe_moe_forward_host.argtypes = [vp, vp, vp, i]
     L.zmoe_get_routes.argtypes = [vp, i, i, vp, vp]
@@ -225,6 +226,11 @@ class Layer:
         check(load().zmoe_expert_ffn_events(self.h, ptr(out), out.shape[0], 0, _stream_ptr(stream),
                                             C.c_void_p(ev0.cuda_event), C.c_void_p(ev1.cuda_event)),
               "zmoe_expert_ffn_events")
+
+    def dense_ffn(self, x, out, accumulate=0, stream=None):
+        """single-expert layer applied to every token (shared expert)"""
+        check(load().zmoe_dense_ffn(self.h, ptr(x), ptr(out), x.shape[0], accumulate, _stream_ptr(stream)),
+              "zmoe_dense_ffn")
 
     def forward(self, x, out, stream=None):
         check(load().zmoe_moe_forward(self.h, ptr(x), ptr(out), x.shape[0], _stream_ptr(stream)), "zmoe_moe_forward")
