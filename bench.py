@@ -263,6 +263,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra batch sizes of the sweep")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill-shaped probe")
+    ap.add_argument("--path", type=int, default=0, help="zmoe_ctx_set_path for the decode stack (0 = the library's choice)")
     ap.add_argument("--prefill-only", action="store_true", help="run only the prefill-shaped probe (profiler captures)")
     ap.add_argument("--prefill-experts", type=int, default=E)
     ap.add_argument("--prefill-tokens", type=int, default=4096)
@@ -299,6 +300,8 @@ def main():
     n_local = e_hi - e_lo
     t_all = T * world
     ctx = lib.Context(max(t_all, 16), D, F, E, K)
+    if args.path:
+        ctx.set_path(args.path)
     layers, weights = [], []
     for l in range(LAYERS):
         wg, wu, wd, wr = make_layer_weights(args.seed, l, dev, e_lo, e_hi)

@@ -201,7 +201,9 @@ int zmoe_get_act(zmoe_ctx *ctx, int n_pairs, int d_ff, float *act_host);
 /* which expert-FFN kernels run: 0 = choose by shape (tensor-core grouped GEMM once the call
  * averages 24 or more pairs per expert, decode kernels below that), 1 = decode kernels,
  * 2 = tensor-core GEMM whenever the shapes allow (rows per expert a multiple of 128, gate and
- * up of one type).  The activations passed to zmoe_route / zmoe_set_routes must stay valid
+ * up of one type), 3 = decode kernels with one pair at a time (a pair's result then does not
+ * depend on which other pairs share its expert; slower once experts hold several pairs).
+ * The activations passed to zmoe_route / zmoe_set_routes must stay valid
  * until zmoe_expert_ffn has been enqueued. */
 int zmoe_ctx_set_path(zmoe_ctx *ctx, int path);
 /* reads and clears the device error flag: 0, or ZMOE_ERR_DEVICE_WAIT */

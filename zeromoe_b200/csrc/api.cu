@@ -81,7 +81,7 @@ struct zmoe_ctx {
     int32_t *zero_ids = nullptr;   // [T] zeros / ones: routes of a dense (single-expert) FFN
     float *one_w = nullptr;
     const float *x_last = nullptr;  // the activations the current route table was built from
-    int path = 0;              // 0 auto, 1 decode kernels, 2 tensor-core GEMM
+    int path = 0;              // 0 auto, 1 decode kernels, 2 tensor-core GEMM, 3 decode kernels, scalar path only
     float *ydown = nullptr;    // [P, D] per-pair down-projection output
     float *logits = nullptr;   // [T, E] router logits, then probabilities
     int32_t *ids = nullptr;    // [T, K]
@@ -98,6 +98,8 @@ struct zmoe_layer {
     zmoe_ctx *ctx;
     zmoe_layer_desc d;
     MmidGeom g_gu, g_gate1, g_dn;
+    CUtensorMap tm_gate, tm_up, tm_down;   // padded-row tile maps, where the geometry pads rows
+    bool has_tm_gu = false, has_tm_dn = false;
     bool dual;
     size_t bytes_gate, bytes_up, bytes_down;
     int nrt_gu, nrt_dn;
@@ -211,6 +213,16 @@ int zmoe_layer_create(zmoe_ctx *ctx, const zmoe_layer_desc *desc, zmoe_layer **o
     }
     L->nrt_gu = (d.d_ff + L->g_gu.R - 1) / L->g_gu.R;
     L->nrt_dn = (d.d_model + L->g_dn.R - 1) / L->g_dn.R;
+    {
+        const int rb_gu = (d.d_model / QK_K) * block_bytes(d.gate.type), rb_dn = (d.d_ff / QK_K) * block_bytes(d.down.type);
+        if (L->dual && L->g_gu.rbs != rb_gu)
+            L->has_tm_gu =
+                make_rows_map(&L->tm_gate, d.gate.data_dev, d.n_experts, d.d_ff, rb_gu, d.gate.expert_stride, L->g_gu.R) == ZMOE_OK &&
+                make_rows_map(&L->tm_up, d.up.data_dev, d.n_experts, d.d_ff, rb_gu, d.up.expert_stride, L->g_gu.R) == ZMOE_OK;
+        if (L->g_dn.rbs != rb_dn)
+            L->has_tm_dn = make_rows_map(&L->tm_down, d.down.data_dev, d.n_experts, d.d_model, rb_dn, d.down.expert_stride,
+                                         L->g_dn.R) == ZMOE_OK;
+    }
     *out = L;
     return ZMOE_OK;
 }
@@ -285,6 +297,7 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
     m.n_sm = c->n_sm;
     m.clamp = d.swiglu_clamp;
     m.clamp_fused = d.swiglu_clamp_fused;
+    m.multi = T > 1 && c->path != 3;
     int rc;
     // many pairs per expert: the contraction is compute-bound and goes to the tensor cores
     const bool gemm_ok = L->dual && c->x_last && gemm_sm100_supported(d.gate.type, d.d_model, d.d_ff) &&
@@ -326,7 +339,9 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         m.q8 = c->q8x; m.xdiv = d.topk;
         m.y = c->act; m.ldy = d.d_ff;
         m.down = false;
+        if (L->has_tm_gu) { m.tm0 = &L->tm_gate; m.tm1 = &L->tm_up; }
         rc = launch_mmid(m, L->g_gu, st);
+        m.tm0 = nullptr; m.tm1 = nullptr;
         g_launches += 1;
     } else {
         float *gbuf = c->act2, *ubuf = c->act2 + (size_t)P * d.d_ff;
@@ -355,6 +370,7 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         m.q8 = c->q8act; m.xdiv = 1;
         m.y = c->ydown; m.ldy = d.d_model;
         m.down = true;
+        if (L->has_tm_dn) m.tm0 = &L->tm_down;
         rc = launch_mmid(m, L->g_dn, st);
     }
     if (!rc) rc = launch_combine(out_dev, c->ydown, c->weights, c->ids, T, d.topk, d.d_model, d.n_experts, accumulate, st);
@@ -423,7 +439,7 @@ int zmoe_get_act(zmoe_ctx *c, int n_pairs, int d_ff, float *act_host) {
 }
 
 int zmoe_ctx_set_path(zmoe_ctx *c, int path) {
-    if (!c || path < 0 || path > 2) return ZMOE_ERR_ARG;
+    if (!c || path < 0 || path > 3) return ZMOE_ERR_ARG;
     c->path = path;
     return ZMOE_OK;
 }
@@ -519,6 +535,7 @@ int dense_matmul(int type, float *y, const float *x, int ldx, const void *w, int
     m.clamp = 0.f; m.clamp_fused = 0;
     m.err = s->err;
     m.n_sm = s->n_sm;
+    m.multi = S > 1;
     rc = launch_mmid(m, g, st);
     g_launches += 3;
     return rc;
@@ -615,6 +632,7 @@ bool zmoe_f32_quant_hook(const zmoe_tensor *w, const zmoe_tensor *x, const zmoe_
         m.plan = s->plan.b; m.down = false;
         m.clamp = 0.f; m.clamp_fused = 0;
         m.err = s->err; m.n_sm = s->n_sm;
+        m.multi = T > 1;
         if (!rc) rc = launch_mmid(m, g, st);
         if (!rc) fill_bad_rows(m.y, m.ldy, s->ids, K * T, E, O, st);
         g_launches += 5;

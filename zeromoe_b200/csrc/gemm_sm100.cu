@@ -137,6 +137,21 @@ static int make_x_map(CUtensorMap *m, const void *base, int rows, int cols) {
     return r == CUDA_SUCCESS ? ZMOE_OK : ZMOE_ERR_CUDA;
 }
 
+int make_rows_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t expert_stride, int R) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return ZMOE_ERR_CUDA;
+    // rows as 8-byte elements: a box row is one contiguous run, two elements longer than the row
+    if (rb % 16 || expert_stride % 16 || rb / 8 + 2 > 256 || R > 256) return ZMOE_ERR_SHAPE;
+    const cuuint64_t dims[3] = {(cuuint64_t)(rb / 8), (cuuint64_t)O, (cuuint64_t)E};
+    const cuuint64_t strides[2] = {(cuuint64_t)rb, (cuuint64_t)expert_stride};
+    const cuuint32_t box[3] = {(cuuint32_t)(rb / 8 + 2), (cuuint32_t)R, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void *>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? ZMOE_OK : ZMOE_ERR_CUDA;
+}
+
 int launch_gemm_sm100(const GemmLaunch &L, cudaStream_t st) {
     if (!gemm_sm100_supported(L.type, L.I, L.O)) return ZMOE_ERR_SHAPE;
     GemmFn fn = nullptr;

@@ -22,7 +22,7 @@ int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
         g->upl = (U + 31) / 32;
     }
     // must match the instantiations in pick(): consumer warps per (lanes per row, units per lane)
-    g->ncw = g->lpr == 16 ? 12 : g->upl <= 2 ? 16 : g->upl == 3 ? 12 : 8;
+    g->ncw = g->upl <= 2 ? 16 : g->upl == 3 ? 12 : 8;
     const int rb = (I / QK_K) * bb;
     const int rpw = 32 / g->lpr;
     int unit = rpw * g->ncw;  // rows of one full pass of the consumer warps
@@ -31,14 +31,22 @@ int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
     while ((ralign * rb) % 16 != 0) ralign *= 2;
     while (unit % ralign != 0) unit *= 2;
     const int ntile = dual ? 2 : 1;
-    const int q8s = q8row_stride(I);
+    // Shared-memory strides.  The multi-token path reads 8 rows x 4 consecutive words per load and
+    // 4 activation rows x 4 words: a row stride of 4 (mod 8) words and an activation stride that is not
+    // a multiple of 16 words keep those loads free of bank conflicts.  Padding weight rows needs one
+    // copy per row, so rows must be multiples of 16 bytes.
+    int rbs = rb, q8s = q8row_stride(I);
+    if ((type == Q2_K || type == Q3_K) && rb % 16 == 0)
+        while ((rbs / 4) % 8 != 4) rbs += 16;   // at most one step: rb + 16, what make_rows_map delivers
+    while ((q8s / 4) % 16 == 0) q8s += 16;
+    g->rbs = rbs; g->q8s = q8s;
     const int budget = 200 * 1024;
     int R = unit;
     // grow towards ~40 KB of weights per stage while at least three stages fit
-    while ((size_t)ntile * (R + unit) * rb <= 40 * 1024 && R + unit <= O + unit - 1) R += unit;
+    while ((size_t)ntile * (R + unit) * rbs <= 40 * 1024 && R + unit <= O + unit - 1) R += unit;
     for (;;) {
         g->R = R;
-        g->wtile_bytes = (R * rb + 16 + 16 + 127) & ~127;
+        g->wtile_bytes = (R * rbs + 16 + 16 + 127) & ~127;
         g->stage_bytes = (ntile * g->wtile_bytes + MMID_MAXTOK * q8s + 127) & ~127;
         g->nstage = budget / g->stage_bytes;
         if (g->nstage > MMID_MAXSTAGE) g->nstage = MMID_MAXSTAGE;
@@ -53,44 +61,58 @@ int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
 
 using KernelFn = void (*)(const MmidParams);
 
-template <int TYPE, bool DUAL>
+template <int TYPE, bool DUAL, bool MMA>
 static KernelFn pick(int lpr, int upl) {
     if (lpr == 8) {
         switch (upl) {
-        case 1: return mmid_kernel<TYPE, 8, 1, DUAL, 16>;
-        case 2: return mmid_kernel<TYPE, 8, 2, DUAL, 16>;
-        case 3: return mmid_kernel<TYPE, 8, 3, DUAL, 12>;
-        case 4: return mmid_kernel<TYPE, 8, 4, DUAL, 8>;
-        }
-    } else if (lpr == 16) {
-        switch (upl) {
-        case 3: return mmid_kernel<TYPE, 16, 3, DUAL, 12>;
-        case 4: return mmid_kernel<TYPE, 16, 4, DUAL, 12>;
+        case 1: return mmid_kernel<TYPE, 8, 1, DUAL, 16, MMA>;
+        case 2: return mmid_kernel<TYPE, 8, 2, DUAL, 16, MMA>;
+        case 3: return mmid_kernel<TYPE, 8, 3, DUAL, 12, MMA>;
+        case 4: return mmid_kernel<TYPE, 8, 4, DUAL, 8, MMA>;
         }
     } else {
         switch (upl) {
-        case 1: return mmid_kernel<TYPE, 32, 1, DUAL, 16>;
-        case 2: return mmid_kernel<TYPE, 32, 2, DUAL, 16>;
-        case 3: return mmid_kernel<TYPE, 32, 3, DUAL, 12>;
-        case 4: return mmid_kernel<TYPE, 32, 4, DUAL, 8>;
+        case 1: return mmid_kernel<TYPE, 32, 1, DUAL, 16, MMA>;
+        case 2: return mmid_kernel<TYPE, 32, 2, DUAL, 16, MMA>;
+        case 3: return mmid_kernel<TYPE, 32, 3, DUAL, 12, MMA>;
+        case 4: return mmid_kernel<TYPE, 32, 4, DUAL, 8, MMA>;
         }
     }
     return nullptr;
 }
 
 template <bool DUAL>
-static KernelFn pick_type(int type, int lpr, int upl) {
+static KernelFn pick_type(int type, int lpr, int upl, bool mma) {
     switch (type) {
-    case Q2_K: return pick<Q2_K, DUAL>(lpr, upl);
-    case Q3_K: return pick<Q3_K, DUAL>(lpr, upl);
-    case Q4_K: return pick<Q4_K, DUAL>(lpr, upl);
-    case IQ2_XXS: return pick<IQ2_XXS, DUAL>(lpr, upl);
+    case Q2_K: return mma ? pick<Q2_K, DUAL, true>(lpr, upl) : pick<Q2_K, DUAL, false>(lpr, upl);
+    case Q3_K: return mma ? pick<Q3_K, DUAL, true>(lpr, upl) : pick<Q3_K, DUAL, false>(lpr, upl);
+    case Q4_K: return pick<Q4_K, DUAL, false>(lpr, upl);
+    case IQ2_XXS: return pick<IQ2_XXS, DUAL, false>(lpr, upl);
     }
     return nullptr;
 }
 
+// The multi-token path splits a tile into 16-row pieces and each piece's row into slices of whole
+// half super-blocks, one slice per warp; it needs every output of a tile to find a thread.
+static bool mma_split(int type, const MmidGeom &g, int I, int *ks, int *hpw) {
+    if (type != Q2_K && type != Q3_K) return false;
+    if (g.R % 16 != 0) return false;
+    // rows must start on word boundaries, the same for every lane of a fragment load
+    if (((I / QK_K) * block_bytes(type)) % 4 != 0) return false;
+    const int pieces = g.R / 16;
+    if (pieces > g.ncw || MMID_MAXTOK * g.R > 32 * g.ncw) return false;
+    const int nhb = I / 128;
+    *ks = 1;   // a power of two
+    while (*ks * 2 * pieces <= g.ncw && *ks * 2 <= nhb) *ks *= 2;
+    *hpw = (nhb + *ks - 1) / *ks;
+    if (type == Q2_K) *hpw = (*hpw + 1) & ~1;   // whole super-blocks per warp (MmaPath<Q2_K>::kGrain)
+    return true;
+}
+
 int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
-    KernelFn fn = L.dual ? pick_type<true>(L.type, g.lpr, g.upl) : pick_type<false>(L.type, g.lpr, g.upl);
+    int mma_ks = 0, mma_hpw = 0;
+    const bool mma = L.multi && mma_split(L.type, g, L.I, &mma_ks, &mma_hpw);
+    KernelFn fn = L.dual ? pick_type<true>(L.type, g.lpr, g.upl, mma) : pick_type<false>(L.type, g.lpr, g.upl, mma);
     if (!fn) return ZMOE_ERR_TYPE;
     if ((reinterpret_cast<size_t>(L.w0) & 15) || (L.dual && (reinterpret_cast<size_t>(L.w1) & 15))) return ZMOE_ERR_ALIGN;
     // the opt-in shared-memory limit is a per-function, per-device attribute: raise it once
@@ -115,6 +137,14 @@ int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
     p.total0 = L.total0; p.total1 = L.total1;
     p.I = L.I; p.O = L.O;
     p.rb = (L.I / QK_K) * block_bytes(L.type);
+    // padded rows need the tiled maps; without them tiles are dense
+    p.use_tmap = g.rbs != p.rb && L.tm0 && (!L.dual || L.tm1);
+    p.rbs = p.use_tmap ? g.rbs : p.rb;
+    p.q8s = g.q8s;
+    if (p.use_tmap) {
+        p.tm0 = *L.tm0;
+        if (L.dual) p.tm1 = *L.tm1;
+    }
     p.R = g.R;
     p.q8 = L.q8;
     p.q8_stride = q8row_stride(L.I);
@@ -126,6 +156,10 @@ int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
     p.hdr_items = L.down ? 2 : 1;
     p.clamp = L.clamp; p.clamp_fused = L.clamp_fused;
     p.nstage = g.nstage; p.stage_bytes = g.stage_bytes; p.wtile_bytes = g.wtile_bytes;
+    p.mma_ks_log2 = 0;
+    while ((1 << p.mma_ks_log2) < mma_ks) ++p.mma_ks_log2;
+    p.mma_hpw = mma_hpw;
+    p.mma_rdiv = (65536 + g.R - 1) / g.R;
     p.err = L.err;
     return launch_pdl(fn, dim3(L.n_sm), dim3(32 * (g.ncw + 1)), g.smem_bytes, st, p) == cudaSuccess ? ZMOE_OK
                                                                                                    : ZMOE_ERR_CUDA;

@@ -20,6 +20,9 @@
 // Every wait is bounded; on expiry the CTA raises an error flag and unwinds.
 #pragma once
 
+#include <cuda.h>
+
+#include "mmid_mma.cuh"
 #include "quant_units.cuh"
 
 namespace zmoe {
@@ -47,6 +50,8 @@ struct MmidParams {
     size_t total0, total1;      // bytes addressable from w0 / w1
     int I, O;                   // elements per row, rows per expert
     int rb;                     // bytes per weight row
+    int rbs;                    // bytes between rows of a tile in shared memory (>= rb; > rb: one copy per row)
+    int q8s;                    // bytes between the item's activation rows in shared memory (>= q8_stride)
     int R;                      // rows per tile
     const uint8_t *q8;          // packed activation rows
     int q8_stride;              // bytes per packed row
@@ -60,8 +65,21 @@ struct MmidParams {
     int nstage;
     int stage_bytes;            // bytes per ring stage (multiple of 128)
     int wtile_bytes;            // bytes reserved per weight tile inside a stage (multiple of 128)
+    int mma_ks_log2;            // multi-token path: log2 of the warps that share one 16-row piece
+    int mma_hpw;                // multi-token path: half super-blocks per warp
+    int mma_rdiv;               // multi-token path: ceil(65536 / R), for dividing a thread index by R
     int *err;                   // device error flag
+    int use_tmap;               // tiles come through tm0 / tm1 (rows padded to rbs = rb + 16 by the copy)
+    alignas(64) CUtensorMap tm0, tm1;
 };
+
+// 3-D tiled copy (no multicast): box of the map at (0, row, expert)
+__device__ __forceinline__ void tma_load_rows(void *dst_smem, const void *tmap, int row, int expert, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(dst_smem)), "l"(tmap), "r"(0), "r"(row), "r"(expert), "r"(smem_u32(bar))
+        : "memory");
+}
 
 struct StageMeta {
     int expert, r0, nrows, ntok;
@@ -109,8 +127,10 @@ __device__ __forceinline__ uint32_t issue_tile(uint8_t *dst, const uint8_t *w, s
     return bytes;
 }
 
-template <int TYPE, int LPR, int UPL, bool DUAL, int NCW>
-__global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParams p) {
+// MMA: items with two or more pairs take the tensor-core path of mmid_mma.cuh; the activation
+// registers of the scalar path are then not kept from one item to the next.
+template <int TYPE, int LPR, int UPL, bool DUAL, int NCW, bool MMA>
+__global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const __grid_constant__ MmidParams p) {
     constexpr int BB = QTraits<TYPE>::kBytes;
     constexpr int RPW = 32 / LPR;  // rows a warp handles at once
     extern __shared__ __align__(128) uint8_t smem[];
@@ -118,6 +138,10 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
     __shared__ StageMeta meta[MMID_MAXSTAGE];
     __shared__ __align__(8) uint64_t iq2_grid[TYPE == IQ2_XXS ? 256 : 1], iq2_sign[TYPE == IQ2_XXS ? 128 : 1];
 
+    // multi-token path: per-warp partial sums [buffer][warp][matrix][16 rows][MAXTOK pairs], double buffered
+    constexpr int PART = 16 * MMID_MAXTOK * (DUAL ? 2 : 1);
+    __shared__ __align__(16) float part[MMA ? 2 : 1][MMA ? NCW : 1][MMA ? PART : 1];
+    __shared__ __align__(8) uint64_t part_bar;
     __shared__ int s_item_offs[MMID_PLAN_SMEM + 1], s_active[MMID_PLAN_SMEM], s_aoffs[MMID_PLAN_SMEM],
         s_antok[MMID_PLAN_SMEM];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -127,6 +151,7 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], NCW);
         }
+        mbar_init(&part_bar, NCW);
         mbar_init_fence();
     }
     if (TYPE == IQ2_XXS) iq2_fill_tables(iq2_grid, iq2_sign);
@@ -213,7 +238,18 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
                 uint8_t *stage = smem + (size_t)s * p.stage_bytes;
                 uint8_t *q8dst = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
                 uint32_t bytes = 0;
-                if (lane == 0) {
+                if (p.use_tmap) {
+                    // one tiled copy per tile; the box is always R full padded rows (rows past the
+                    // expert's last arrive as zeros)
+                    if (lane == 0) {
+                        StageMeta &m = meta[s];
+                        m.expert = je; m.r0 = jr0; m.nrows = jnrows; m.ntok = jntok;
+                        m.w0_off = 0; m.w1_off = 0;
+                        tma_load_rows(stage, &p.tm0, jr0, je, &full_bar[s]);
+                        if (DUAL) tma_load_rows(stage + p.wtile_bytes, &p.tm1, jr0, je, &full_bar[s]);
+                        bytes = (uint32_t)(p.R * p.rbs) * (DUAL ? 2u : 1u);
+                    }
+                } else if (lane == 0) {
                     StageMeta &m = meta[s];
                     m.expert = je; m.r0 = jr0; m.nrows = jnrows; m.ntok = jntok;
                     const size_t g0 = (size_t)je * p.stride0 + (size_t)jr0 * p.rb;
@@ -231,7 +267,7 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
                     const int xr = my_pair / p.xdiv;
                     meta[s].pair[lane] = my_pair;
                     meta[s].xrow[lane] = xr;
-                    bulk_g2s(q8dst + (size_t)lane * p.q8_stride, p.q8 + (size_t)xr * p.q8_stride,
+                    bulk_g2s(q8dst + (size_t)lane * p.q8s, p.q8 + (size_t)xr * p.q8_stride,
                              (uint32_t)p.q8_stride, &full_bar[s]);
                 }
                 __syncwarp();
@@ -252,6 +288,7 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
         float park0 = 0.f, park1 = 0.f;
         size_t park_idx = 0;
         int parked = 0;
+        int n_mma = 0;   // multi-token items so far: the same in every consumer warp
         auto flush = [&]() {
             if (sl < parked) {
                 float a0 = park0, a1 = park1;
@@ -259,6 +296,35 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
                 if (park_idx != (size_t)-1) p.y[park_idx] = DUAL ? swiglu_f(a0, a1, p.clamp, p.clamp_fused) : a0;
             }
             parked = 0;
+        };
+        // output this thread owes for the last multi-token item (roles are recomputed where needed
+        // rather than kept in registers through the scalar path)
+        bool pend = false, pend_on = false;
+        size_t pend_idx = 0;
+        const int ks_n = 1 << p.mma_ks_log2;
+        // final sums: thread t of the consumer warps owns output t of the tile (pair t / R, row t % R)
+        auto out_role = [&](int &o_tok, int &o_row) {
+            const int ot = warp * 32 + lane;
+            o_tok = (ot * p.mma_rdiv) >> 16;   // ot / R for ot < 1024
+            o_row = ot - o_tok * p.R;
+        };
+        auto finish_pending = [&]() -> bool {
+            if (!pend) return true;
+            pend = false;
+            const int q = n_mma - 1;
+            if (!mbar_wait(&part_bar, q & 1)) return false;
+            if (pend_on) {
+                int o_tok, o_row;
+                out_role(o_tok, o_row);
+                const float *pr = &part[q & 1][0][0] + ((o_row >> 4) << p.mma_ks_log2) * PART + (o_row & 15) * MMID_MAXTOK + o_tok;
+                float a0 = 0.f, a1 = 0.f;
+                for (int i = 0; i < ks_n; ++i) {
+                    a0 += pr[i * PART];
+                    if (DUAL) a1 += pr[i * PART + 64];
+                }
+                p.y[pend_idx] = DUAL ? swiglu_f(a0, a1, p.clamp, p.clamp_fused) : a0;
+            }
+            return true;
         };
         for (int k = 0; k < n_mine && ok; ++k) {
             const int s = k % nstage;
@@ -273,14 +339,62 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
             const uint32_t t0 = stage + m.w0_off;
             const uint32_t t1 = stage + p.wtile_bytes + m.w1_off;
             const uint32_t q8base = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
+            if (MMA && m_ntok >= 2 && ((t0 | (DUAL ? t1 : 0u)) & (QTraits<TYPE>::kAlign >= 4 ? 3u : 1u)) == 0) {
+                // ---- multi-token item: warp = (16-row piece ti, slice [hb0, hb1) of the row) ----
+                const int ti = warp >> p.mma_ks_log2;
+                const int hb0 = (warp & (ks_n - 1)) * p.mma_hpw, hb1 = min(hb0 + p.mma_hpw, p.I / 128);
+                // role in the final reduction, read before the stage is released
+                int o_tok, o_row;
+                out_role(o_tok, o_row);
+                const bool o_on = o_tok < m_ntok && o_row < m_nrows;
+                const size_t o_idx = o_on ? (size_t)m.pair[o_tok] * p.ldy + m_r0 + o_row : 0;
+                float f0[4] = {0.f, 0.f, 0.f, 0.f}, f1[4] = {0.f, 0.f, 0.f, 0.f};
+                if (ti * 16 < m_nrows && hb0 < hb1) {
+                    // gate and up one after the other: sharing the activation fragments between them
+                    // costs more registers than the kernel has
+                    mma_rows<TYPE, false>(t0 + (uint32_t)(ti * 16) * p.rbs, 0, p.rbs, q8base, p.q8s, p.I, hb0, hb1, lane, f0, f0);
+                    if (DUAL)
+                        mma_rows<TYPE, false>(t1 + (uint32_t)(ti * 16) * p.rbs, 0, p.rbs, q8base, p.q8s, p.I, hb0, hb1, lane, f1, f1);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[s]);
+                // the previous multi-token item is finished first: its phase of part_bar must be over
+                // before this warp arrives for the next one
+                if (!finish_pending()) {
+                    if (lane == 0) atomicExch(p.err, 3);
+                    ok = false;
+                    break;
+                }
+                // partial sums of this warp: lanes with c < 2 hold pairs 2c, 2c+1 of rows g and g+8
+                float *pw = part[n_mma & 1][warp];
+                {
+                    const int g = lane >> 2, c = lane & 3;
+                    if (c < MMID_MAXTOK / 2) {
+                        *reinterpret_cast<float2 *>(pw + g * MMID_MAXTOK + 2 * c) = make_float2(f0[0], f0[1]);
+                        *reinterpret_cast<float2 *>(pw + (g + 8) * MMID_MAXTOK + 2 * c) = make_float2(f0[2], f0[3]);
+                        if (DUAL) {
+                            *reinterpret_cast<float2 *>(pw + 64 + g * MMID_MAXTOK + 2 * c) = make_float2(f1[0], f1[1]);
+                            *reinterpret_cast<float2 *>(pw + 64 + (g + 8) * MMID_MAXTOK + 2 * c) = make_float2(f1[2], f1[3]);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&part_bar);
+                // the sums are added up one item later (finish_pending), when every warp's slice has long
+                // arrived.  The buffer written two items ago is free: a warp gets here only after the wait
+                // for the previous item's phase, which every warp joins after its reads of the one before.
+                pend = true; pend_on = o_on; pend_idx = o_idx;
+                ++n_mma;
+                continue;
+            }
             for (int tk = 0; tk < m_ntok; ++tk) {
                 const int pair = m.pair[tk];
                 const int xrow = m.xrow[tk];
-                if (xrow != cached_row) {
+                if (MMA || xrow != cached_row) {
 #pragma unroll
                     for (int i = 0; i < UPL; ++i) {
                         const int u = sl + LPR * i;
-                        if (u < U) load_unit_act<TYPE>(q8base + tk * p.q8_stride, p.I, u, act[i]);
+                        if (u < U) load_unit_act<TYPE>(q8base + tk * p.q8s, p.I, u, act[i]);
                     }
                     cached_row = xrow;
                 }
@@ -295,7 +409,7 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
                             if (u < U) {
                                 int is, ms;
                                 float d, dm;
-                                const uint32_t boff = (uint32_t)rr * p.rb + (uint32_t)(u >> 2) * BB;
+                                const uint32_t boff = (uint32_t)rr * p.rbs + (uint32_t)(u >> 2) * BB;
                                 unit_dot<TYPE>(t0 + boff, u & 3, act[i], tb, is, ms, d, dm);
                                 acc0 = fmaf(d * act[i].d, (float)is, acc0);
                                 if (QTraits<TYPE>::kHasMin) acc0 = fmaf(-(dm * act[i].d), (float)ms, acc0);
@@ -324,6 +438,7 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const MmidParam
             if (lane == 0) mbar_arrive(&empty_bar[s]);
         }
         flush();
+        if (MMA && ok && !finish_pending() && lane == 0) atomicExch(p.err, 3);
     }
 }
 

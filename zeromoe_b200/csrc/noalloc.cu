@@ -102,5 +102,6 @@ extern "C" int zmoe_matmul_noalloc(int type, float *y, const float *x, const voi
     m.clamp = 0.f; m.clamp_fused = 0;
     m.err = reinterpret_cast<int *>(base + kOffErr);
     m.n_sm = n_sm;
+    m.multi = S > 1;
     return launch_mmid(m, g, st);
 }

@@ -2,6 +2,7 @@
 // library (not part of the public C ABI; see include/zmoe_b200.h for that).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -42,6 +43,7 @@ struct MmidGeom {
     int lpr, upl, ncw;     // lanes per row, units per lane, consumer warps
     int R;                 // rows per tile
     int nstage, stage_bytes, wtile_bytes;
+    int rbs, q8s;          // shared-memory strides of weight rows and of activation rows
     size_t smem_bytes;
 };
 int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g);
@@ -62,7 +64,13 @@ struct MmidLaunch {
     int clamp_fused;
     int *err;
     int n_sm;
+    bool multi = false;    // some expert may hold two or more pairs: allow the tensor-core consumer path
+    // optional tiled maps of w0 / w1 (make_rows_map) that deliver tiles with padded rows in one copy
+    const CUtensorMap *tm0 = nullptr, *tm1 = nullptr;
 };
+// Map of a [E][O rows][rb bytes] weight tensor whose box is R rows of rb + 16 bytes: the 16 bytes past the
+// end of a row are out of bounds and arrive as zeros, which pads the rows in shared memory.  Rows up to 2032 bytes.
+int make_rows_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t expert_stride, int R);
 int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st);
 
 // prefill path: tcgen05 grouped GEMM over fp16 activations (Q8_K round trip applied, rows scaled)

@@ -140,7 +140,7 @@ class Context:
         check(load().zmoe_ctx_check(self.h), "zmoe_ctx_check")
 
     def set_path(self, path):
-        """0 auto, 1 decode kernels, 2 tensor-core GEMM"""
+        """0 auto, 1 decode kernels, 2 tensor-core GEMM, 3 decode kernels one pair at a time"""
         check(load().zmoe_ctx_set_path(self.h, path), "zmoe_ctx_set_path")
 
     def routes(self, T, K):
