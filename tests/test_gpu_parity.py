@@ -321,6 +321,54 @@ def test_prefill_tensor_core_path_vs_oracle(zlib, oracle, dev, case):
     assert np.array_equal(out2.cpu().numpy().view(np.uint32), outs[2].view(np.uint32))   # reproducible
 
 
+@pytest.mark.parametrize("types", [(synth.Q2_K, synth.Q2_K, synth.Q3_K), (synth.Q3_K, synth.Q3_K, synth.Q2_K)])
+def test_experts_holding_one_to_nine_pairs(zlib, oracle, dev, types):
+    """Experts with 2+ pairs take the tensor-core consumer path, 4 pairs per item: pin the pair count of
+    every expert (1..9, so one-, two- and three-item experts with full and ragged last items), with a
+    ragged last row tile in the down projection, and compare with the oracle and with the one-pair-at-a-time path."""
+    import torch
+    D, F, E, K = 1024, 1536, 9, 3          # the down projection's 1024 rows leave a ragged last 48-row tile
+    counts = list(range(1, E + 1))         # expert e holds e + 1 pairs
+    T = sum(counts) // K                   # 45 pairs = 15 tokens x 3 routes
+    assert T * K == sum(counts)
+    rng = synth.rng_for(23, types[0])
+    # deal the experts' pairs to tokens so that no token gets one expert twice
+    pool = [e for e, n in enumerate(counts) for _ in range(n)]
+    ids = None
+    for _ in range(1000):
+        perm = rng.permutation(len(pool))
+        cand = np.array(pool)[perm].reshape(T, K)
+        if all(len(set(r)) == K for r in cand):
+            ids = cand.astype(np.int32)
+            break
+    assert ids is not None
+    wg = synth.expert_weights(types[0], E, F, D, rng)
+    wu = synth.expert_weights(types[1], E, F, D, rng)
+    wd = synth.expert_weights(types[2], E, D, F, rng)
+    x = synth.activations(T, D, rng)
+    wts = rng.uniform(0.05, 0.6, size=(T, K)).astype(np.float32)
+    ctx = zlib.Context(16, D, F, E, K)
+    layer = zlib.Layer(ctx, D, F, E, K, types, to_dev(wg, dev), to_dev(wu, dev), to_dev(wd, dev))
+    xd, idd, wtd = to_dev(x, dev), to_dev(ids, dev), to_dev(wts, dev)
+    outs = {}
+    for path in (0, 3):
+        ctx.set_path(path)
+        layer.set_routes(xd, idd, wtd)
+        out = torch.full((T, D), float("nan"), device=dev)
+        layer.expert_ffn(out)
+        _sync()
+        ctx.check()
+        outs[path] = (out.cpu().numpy(), ctx.act(T * K, F).reshape(T, K, F).copy())
+    ctx.set_path(0)
+    Lr = oracle.make_layer(D, F, E, K, types, wg, wu, wd)
+    ref, act_ref = oracle.moe_ffn(Lr, x, ids, wts, want_act=True)
+    for path, (got, act) in outs.items():
+        assert rel_to_norm(act, act_ref) < REL_TO_NORM, path
+        assert rel_to_norm(got, ref) < REL_TO_NORM, path
+    # the two paths add the same exact integer sums in a different f32 order
+    assert rel_to_norm(outs[0][0], outs[3][0]) < 1e-5
+
+
 def test_moe_layer_supplied_routes_with_inactive_ids(zlib, oracle, dev):
     """negative ids are inactive routes: they contribute a zero row"""
     import torch
