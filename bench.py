@@ -455,9 +455,9 @@ def main():
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_source": which,
                     "avg_launch_ms": gu_ms, "bytes_per_launch": sum(gu_bytes) / LAYERS,
                     # dram__bytes_read + write of this kernel from ncu on a 1-layer capture of the same
-                    # batch: 355.5 MB for 351.0 MB of algorithmic bytes; traffic is proportional to the
+                    # batch: 357.8 MB for 351.0 MB of algorithmic bytes; traffic is proportional to the
                     # distinct experts streamed, so the ratio carries over to a full launch
-                    "traffic": sum(gu_bytes) / LAYERS * (355.49 / 351.0),
+                    "traffic": sum(gu_bytes) / LAYERS * (357.82 / 351.0),
                     "distinct_experts_per_layer": nact}
         step_bytes = sum(gu_bytes) + sum(dn_bytes) + LAYERS * E * D * 4
         layer_roofline = {"algorithmic_bytes_per_step": step_bytes, "achieved": step_bytes / (ms_step * 1e-3) / 1e9,
