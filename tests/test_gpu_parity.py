@@ -369,10 +369,12 @@ def test_experts_holding_one_to_nine_pairs(zlib, oracle, dev, types):
     assert rel_to_norm(outs[0][0], outs[3][0]) < 1e-5
 
 
-def test_moe_layer_supplied_routes_with_inactive_ids(zlib, oracle, dev):
-    """negative ids are inactive routes: they contribute a zero row"""
+@pytest.mark.parametrize("T", [6, 3])
+def test_moe_layer_supplied_routes_with_inactive_ids(zlib, oracle, dev, T):
+    """negative ids are inactive routes: they contribute a zero row.  T = 3 runs the small-batch launches
+    that quantise act and add up the routes inside the matmul kernels."""
     import torch
-    D, F, E, K, T = 1024, 512, 12, 10, 6
+    D, F, E, K = 1024, 512, 12, 10
     types = (synth.Q2_K, synth.Q2_K, synth.Q3_K)
     rng = synth.rng_for(18, 0)
     wg = synth.expert_weights(types[0], E, F, D, rng)
@@ -382,7 +384,7 @@ def test_moe_layer_supplied_routes_with_inactive_ids(zlib, oracle, dev):
     ids = np.stack([rng.permutation(E)[:K] for _ in range(T)]).astype(np.int32)
     ids[0, 3] = -1
     ids[2, :] = -1          # a token with no active route at all
-    ids[5, 9] = -1
+    ids[T - 1, 9] = -1
     wts = rng.uniform(0.05, 0.3, size=(T, K)).astype(np.float32)
     ctx = zlib.Context(8, D, F, E, K)
     layer = zlib.Layer(ctx, D, F, E, K, types, to_dev(wg, dev), to_dev(wu, dev), to_dev(wd, dev))
@@ -402,6 +404,24 @@ def test_moe_layer_supplied_routes_with_inactive_ids(zlib, oracle, dev):
     layer.expert_ffn(base, accumulate=1)
     _sync()
     assert rel_to_norm(base.cpu().numpy(), ref + 1.0) < REL_TO_NORM
+    if T <= 4:
+        # one pair at a time (path 3) a token's result does not depend on the batch it is in: the same
+        # tokens twice in one batch give the same bytes as alone
+        ctx.set_path(3)
+        layer.set_routes(xd, to_dev(ids, dev), to_dev(wts, dev))
+        alone = torch.full((T, D), float("nan"), device=dev)
+        layer.expert_ffn(alone)
+        x2, ids2, w2 = np.concatenate([x, x]), np.concatenate([ids, ids]), np.concatenate([wts, wts])
+        layer.set_routes(to_dev(x2, dev), to_dev(ids2, dev), to_dev(w2, dev))
+        out2 = torch.full((2 * T, D), float("nan"), device=dev)
+        layer.expert_ffn(out2)
+        _sync()
+        ctx.check()
+        both = out2.cpu().numpy()
+        assert np.array_equal(both[:T].view(np.uint32), alone.cpu().numpy().view(np.uint32))
+        assert np.array_equal(both[T:].view(np.uint32), both[:T].view(np.uint32))
+        assert rel_to_norm(both[:T], ref) < REL_TO_NORM
+        ctx.set_path(0)
 
 
 def test_deepseek_shaped_layer_with_shared_expert(zlib, oracle, dev):

@@ -36,7 +36,7 @@ int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
     // a multiple of 16 words keep those loads free of bank conflicts.  Padding weight rows needs one
     // copy per row, so rows must be multiples of 16 bytes.
     int rbs = rb, q8s = q8row_stride(I);
-    if ((type == Q2_K || type == Q3_K) && rb % 16 == 0)
+    if ((type == Q2_K || type == Q3_K || type == Q4_K) && rb % 16 == 0)
         while ((rbs / 4) % 8 != 4) rbs += 16;   // at most one step: rb + 16, what make_rows_map delivers
     while ((q8s / 4) % 16 == 0) q8s += 16;
     g->rbs = rbs; g->q8s = q8s;
@@ -86,7 +86,7 @@ static KernelFn pick_type(int type, int lpr, int upl, bool mma) {
     switch (type) {
     case Q2_K: return mma ? pick<Q2_K, DUAL, true>(lpr, upl) : pick<Q2_K, DUAL, false>(lpr, upl);
     case Q3_K: return mma ? pick<Q3_K, DUAL, true>(lpr, upl) : pick<Q3_K, DUAL, false>(lpr, upl);
-    case Q4_K: return pick<Q4_K, DUAL, false>(lpr, upl);
+    case Q4_K: return mma ? pick<Q4_K, DUAL, true>(lpr, upl) : pick<Q4_K, DUAL, false>(lpr, upl);
     case IQ2_XXS: return pick<IQ2_XXS, DUAL, false>(lpr, upl);
     }
     return nullptr;
@@ -95,7 +95,7 @@ static KernelFn pick_type(int type, int lpr, int upl, bool mma) {
 // The multi-token path splits a tile into 16-row pieces and each piece's row into slices of whole
 // half super-blocks, one slice per warp; it needs every output of a tile to find a thread.
 static bool mma_split(int type, const MmidGeom &g, int I, int *ks, int *hpw) {
-    if (type != Q2_K && type != Q3_K) return false;
+    if (type != Q2_K && type != Q3_K && type != Q4_K) return false;
     if (g.R % 16 != 0) return false;
     // rows must start on word boundaries, the same for every lane of a fragment load
     if (((I / QK_K) * block_bytes(type)) % 4 != 0) return false;
@@ -105,7 +105,7 @@ static bool mma_split(int type, const MmidGeom &g, int I, int *ks, int *hpw) {
     *ks = 1;   // a power of two
     while (*ks * 2 * pieces <= g.ncw && *ks * 2 <= nhb) *ks *= 2;
     *hpw = (nhb + *ks - 1) / *ks;
-    if (type == Q2_K) *hpw = (*hpw + 1) & ~1;   // whole super-blocks per warp (MmaPath<Q2_K>::kGrain)
+    if (type != Q3_K) *hpw = (*hpw + 1) & ~1;   // whole super-blocks per warp (MmaPath<TYPE>::kGrain)
     return true;
 }
 

@@ -9,7 +9,7 @@
 // limits the scalar path; their throughput is not the point.
 //
 // Integer sums are exact, so per super-block they equal those of the scalar path
-// and of reference kernels/quant/kquant_matmul.cu:179-199 (Q2_K), :201-238 (Q3_K);
+// and of reference kernels/quant/kquant_matmul.cu:179-199 (Q2_K), :201-238 (Q3_K), :74-92 (Q4_K);
 // the f32 assembly adds super-blocks in a different order (a warp owns a slice of
 // the row, slices are added in shared memory in warp order).
 //
@@ -189,10 +189,72 @@ __device__ __forceinline__ void q3k_half(uint32_t rowA, uint32_t rowB, int c, co
     for (int i = 0; i < 4; ++i) acc[i] -= 4 * (hi[i] * 128 + lo[i]);
 }
 
+// ---- Q4_K: d @0, dmin @2, scales[12] @4, qs[128] @16 ------------------------------------------------------
+// Byte 32j + i holds element 64j + i in its low nibble and 64j + 32 + i in its high nibble; 32-element
+// sub-block sb = 2j (low) or 2j + 1 (high) has a 6-bit scale and a 6-bit min.  One k32 instruction per
+// sub-block on the nibbles; the scale multiplies the sub-block's sums afterwards.  Activation rows are in
+// the linear layout: element 64u + i is byte i of unit u.
+// rowA / rowB: the block in rows g and g+8; qblk: the column's activation row + unit 4b + 4c;
+// acc: scaled integer sums of the super-block (from zero); mA / mB: the min bytes of sub-blocks 0-3 and 4-7.
+__device__ __forceinline__ void q4k_block(uint32_t rowA, uint32_t rowB, int c, uint32_t qblk, int (&acc)[4],
+                                          uint32_t (&mnA)[2], uint32_t (&mnB)[2]) {
+    uint32_t scA[2], scB[2];
+    {
+        // scales[12] as words s0 s1 s2 (reference kernels/quant/kquant_matmul.cu:41-48): sub-blocks 0-3 take
+        // 6 bits of s0 (scale) and s1 (min); 4-7 take nibbles of s2 plus the top two bits of s0 / s1
+        const uint32_t a0 = ldso<4>(rowA), a1 = ldso<8>(rowA), a2 = ldso<12>(rowA);
+        const uint32_t b0 = ldso<4>(rowB), b1 = ldso<8>(rowB), b2 = ldso<12>(rowB);
+        scA[0] = a0 & 0x3F3F3F3Fu; scA[1] = (a2 & 0x0F0F0F0Fu) | ((a0 >> 2) & 0x30303030u);
+        mnA[0] = a1 & 0x3F3F3F3Fu; mnA[1] = ((a2 >> 4) & 0x0F0F0F0Fu) | ((a1 >> 2) & 0x30303030u);
+        scB[0] = b0 & 0x3F3F3F3Fu; scB[1] = (b2 & 0x0F0F0F0Fu) | ((b0 >> 2) & 0x30303030u);
+        mnB[0] = b1 & 0x3F3F3F3Fu; mnB[1] = ((b2 >> 4) & 0x0F0F0F0Fu) | ((b1 >> 2) & 0x30303030u);
+    }
+    const uint32_t qA = rowA + 4 * c, qB = rowB + 4 * c;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t wa0, wa1, wb0, wb1, bl0, bl1, bh0, bh1;
+        // immediate offsets need literals: one switch arm per j
+        if (j == 0) { wa0 = ldso<16>(qA); wa1 = ldso<32>(qA); wb0 = ldso<16>(qB); wb1 = ldso<32>(qB);
+                      bl0 = ldso<0>(qblk); bl1 = ldso<16>(qblk); bh0 = ldso<32>(qblk); bh1 = ldso<48>(qblk); }
+        else if (j == 1) { wa0 = ldso<48>(qA); wa1 = ldso<64>(qA); wb0 = ldso<48>(qB); wb1 = ldso<64>(qB);
+                           bl0 = ldso<Q8_UNIT_STRIDE>(qblk); bl1 = ldso<Q8_UNIT_STRIDE + 16>(qblk);
+                           bh0 = ldso<Q8_UNIT_STRIDE + 32>(qblk); bh1 = ldso<Q8_UNIT_STRIDE + 48>(qblk); }
+        else if (j == 2) { wa0 = ldso<80>(qA); wa1 = ldso<96>(qA); wb0 = ldso<80>(qB); wb1 = ldso<96>(qB);
+                           bl0 = ldso<2 * Q8_UNIT_STRIDE>(qblk); bl1 = ldso<2 * Q8_UNIT_STRIDE + 16>(qblk);
+                           bh0 = ldso<2 * Q8_UNIT_STRIDE + 32>(qblk); bh1 = ldso<2 * Q8_UNIT_STRIDE + 48>(qblk); }
+        else { wa0 = ldso<112>(qA); wa1 = ldso<128>(qA); wb0 = ldso<112>(qB); wb1 = ldso<128>(qB);
+               bl0 = ldso<3 * Q8_UNIT_STRIDE>(qblk); bl1 = ldso<3 * Q8_UNIT_STRIDE + 16>(qblk);
+               bh0 = ldso<3 * Q8_UNIT_STRIDE + 32>(qblk); bh1 = ldso<3 * Q8_UNIT_STRIDE + 48>(qblk); }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int sb = 2 * j + h;
+            int t[4];
+            mma_u8s8_k32<true>(t, (wa0 >> (4 * h)) & 0x0F0F0F0Fu, (wb0 >> (4 * h)) & 0x0F0F0F0Fu,
+                               (wa1 >> (4 * h)) & 0x0F0F0F0Fu, (wb1 >> (4 * h)) & 0x0F0F0F0Fu, h ? bh0 : bl0, h ? bh1 : bl1);
+            const uint32_t e = 0x4440u | (sb & 3);
+            const int sA = (int)__byte_perm(scA[sb >> 2], 0, e), sB = (int)__byte_perm(scB[sb >> 2], 0, e);
+            acc[0] += sA * t[0]; acc[1] += sA * t[1];
+            acc[2] += sB * t[2]; acc[3] += sB * t[3];
+        }
+    }
+}
+// Sums of the activations over each 32-element sub-block (two adjacent int16 group sums, |v| <= 4064) of
+// sub-blocks 4c'..4c'+3 (c' = c & 1) as byte planes v = 128 * hi + lo.  w: the eight group sums.
+__device__ __forceinline__ void bsum_pair_planes(uint4 w, uint32_t &hi, uint32_t &lo) {
+    const int s0 = (int)(short)(w.x & 0xffffu) + ((int)w.x >> 16), s1 = (int)(short)(w.y & 0xffffu) + ((int)w.y >> 16);
+    const int s2 = (int)(short)(w.z & 0xffffu) + ((int)w.z >> 16), s3 = (int)(short)(w.w & 0xffffu) + ((int)w.w >> 16);
+    lo = (uint32_t)(s0 & 127) | ((uint32_t)(s1 & 127) << 8) | ((uint32_t)(s2 & 127) << 16) | ((uint32_t)(s3 & 127) << 24);
+    hi = (uint32_t)((s0 >> 7) & 255) | ((uint32_t)((s1 >> 7) & 255) << 8) | ((uint32_t)((s2 >> 7) & 255) << 16) |
+         ((uint32_t)((s3 >> 7) & 255) << 24);
+}
+
 template <int TYPE> struct MmaPath { static constexpr bool kHas = false; static constexpr int kGrain = 1; };
 // kGrain: half super-blocks a warp's slice must be a multiple of
 template <> struct MmaPath<Q2_K> { static constexpr bool kHas = true; static constexpr int kGrain = 2; };
 template <> struct MmaPath<Q3_K> { static constexpr bool kHas = true; static constexpr int kGrain = 1; };
+template <> struct MmaPath<Q4_K> { static constexpr bool kHas = true; static constexpr int kGrain = 2; };
 
 // Rows g and g+8 of a 16-row slice against the item's pairs over half-blocks [hb0, hb1): the f32 sums of
 // (row g, pair 2c), (row g, pair 2c+1), (row g+8, pair 2c), (row g+8, pair 2c+1) are added into f0 (tile0)
@@ -238,6 +300,34 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
                 f[1] = fmaf(dA * dx1, (float)cm[1], f[1]); f[1] = fmaf(-(mA * dx1), (float)cn[1], f[1]);
                 f[2] = fmaf(dB * dx0, (float)cm[2], f[2]); f[2] = fmaf(-(mB * dx0), (float)cn[2], f[2]);
                 f[3] = fmaf(dB * dx1, (float)cm[3], f[3]); f[3] = fmaf(-(mB * dx1), (float)cn[3], f[3]);
+            }
+        }
+    } else if (TYPE == Q4_K) {
+        for (int b = hb0 >> 1; b < (hb1 >> 1); ++b) {
+            // group sums of sub-blocks 4c'..4c'+3, c' = c & 1; lanes with c >= 2 multiply them by zero mins
+            uint32_t bs_hi, bs_lo;
+            bsum_pair_planes(lds128(qrow + (uint32_t)q8row_bs_off(I) + 32 * b + 16 * (c & 1)), bs_hi, bs_lo);
+            const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow + q8_stride + 4 * b));
+            const uint32_t qblk = qrow + (uint32_t)(4 * b) * Q8_UNIT_STRIDE + 4 * c;
+            const uint32_t boff = (uint32_t)b * BB;
+#pragma unroll
+            for (int m = 0; m < (DUAL ? 2 : 1); ++m) {
+                const uint32_t rowA = (m ? tile1 : tile0) + offA + boff, rowB = (m ? tile1 : tile0) + offB + boff;
+                float (&f)[4] = m ? f1 : f0;
+                int cm[4], hi[4], cn[4];
+                uint32_t mnA[2], mnB[2];
+                q4k_block(rowA, rowB, c, qblk, cm, mnA, mnB);
+                // k-slots 4c..4c+3 of the k16 instruction = sub-blocks 4c..4c+3: only c = 0, 1 exist
+                const uint32_t fa = c < 2 ? mnA[c & 1] : 0u, fb = c < 2 ? mnB[c & 1] : 0u;
+                mma_k16_zero<false>(hi, fa, fb, bs_hi);
+                mma_k16_zero<false>(cn, fa, fb, bs_lo);
+                const uint32_t wa = lds32(rowA), wb = lds32(rowB);
+                const float dA = half_bits_to_float(wa), mA = half_bits_to_float(wa >> 16);
+                const float dB = half_bits_to_float(wb), mB = half_bits_to_float(wb >> 16);
+                f[0] = fmaf(dA * dx0, (float)cm[0], f[0]); f[0] = fmaf(-(mA * dx0), (float)(cn[0] + 128 * hi[0]), f[0]);
+                f[1] = fmaf(dA * dx1, (float)cm[1], f[1]); f[1] = fmaf(-(mA * dx1), (float)(cn[1] + 128 * hi[1]), f[1]);
+                f[2] = fmaf(dB * dx0, (float)cm[2], f[2]); f[2] = fmaf(-(mB * dx0), (float)(cn[2] + 128 * hi[2]), f[2]);
+                f[3] = fmaf(dB * dx1, (float)cm[3], f[3]); f[3] = fmaf(-(mB * dx1), (float)(cn[3] + 128 * hi[3]), f[3]);
             }
         }
     } else {
