@@ -104,7 +104,7 @@ bool gemm_sm100_supported(int type, int I, int O) {
     return block_bytes(type) != 0 && I > 0 && O > 0 && I % QK_K == 0 && O % GEMM_BM == 0;
 }
 
-using GemmFn = void (*)(const GemmParams, const CUtensorMap);
+using GemmFn = void (*)(const GemmParams, const GemmMaps);
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point: no link against libcuda
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -123,13 +123,13 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// fp16 matrix [rows, cols] row-major, box 64 columns x 256 rows, 128-byte swizzle
-static int make_x_map(CUtensorMap *m, const void *base, int rows, int cols) {
+// fp16 matrix [rows, cols] row-major, box 64 columns x box_rows rows, 128-byte swizzle
+static int make_x_map(CUtensorMap *m, const void *base, int rows, int cols, int box_rows) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return ZMOE_ERR_CUDA;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, (cuuint32_t)GEMM_BN};
+    const cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -185,14 +185,15 @@ int launch_gemm_sm100(const GemmLaunch &L, cudaStream_t st) {
     p.I = L.I; p.O = L.O;
     p.rb = (L.I / QK_K) * block_bytes(L.type);
     p.xscale = L.xscale;
-    CUtensorMap xmap;
-    if (make_x_map(&xmap, L.x_f16, L.x_rows, L.I)) return ZMOE_ERR_CUDA;
+    GemmMaps maps;
+    for (int i = 0; i < 4; ++i)
+        if (make_x_map(&maps.box[i], L.x_f16, L.x_rows, L.I, 32 << i)) return ZMOE_ERR_CUDA;
     p.y = L.y; p.ldy = L.ldy;
     p.hdr = L.plan.hdr; p.active = L.plan.active; p.aoffs = L.plan.aoffs; p.antok = L.plan.antok; p.slot = L.plan.slot;
     p.clamp = L.clamp; p.clamp_fused = L.clamp_fused;
     p.nstage = nstage;
     p.err = L.err;
-    return launch_pdl(fn, dim3(L.n_sm), dim3(GEMM_THREADS), smem, st, p, xmap) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+    return launch_pdl(fn, dim3(L.n_sm), dim3(GEMM_THREADS), smem, st, p, maps) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
 }
 
 }  // namespace zmoe

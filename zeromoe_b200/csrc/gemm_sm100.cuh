@@ -52,9 +52,15 @@ struct GemmParams {
     int *err;
 };
 
+// Activation tile maps with boxes of 32, 64, 128 and 256 rows: a tile loads the smallest box that covers
+// its pairs, so an expert with few pairs does not pull 256 rows through L2 for every k-step.
+struct GemmMaps {
+    alignas(64) CUtensorMap box[4];
+};
+
 template <int TYPE, bool DUAL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_sm100_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
@@ -123,8 +129,11 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) 
         // the same activation rows from L2
         const int nb = local / mblocks;
         m0 = (local % mblocks) * GEMM_BM;
-        p0 = p.aoffs[lo] + nb * GEMM_BN;
-        np = min(GEMM_BN, p.antok[lo] - nb * GEMM_BN);
+        // an expert's pairs are split evenly over its pair blocks (300 pairs: 2 x 160, not 256 + 44)
+        const int cnt = p.antok[lo], nblk = (cnt + GEMM_BN - 1) / GEMM_BN;
+        const int bsz = ((cnt + nblk - 1) / nblk + 15) & ~15;
+        p0 = p.aoffs[lo] + nb * bsz;
+        np = max(0, min(bsz, cnt - nb * bsz));
     };
 
     if (warp < GEMM_PWARPS) {
@@ -158,10 +167,11 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) 
                 uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
                 const int k0 = ks * GEMM_BK;
                 if (tid == 0) {
-                    // the activation tile: rows p0 .. p0+255 of the sorted activations, columns k0 .. k0+63;
-                    // rows past the end of the buffer arrive as zeros
-                    mbar_arrive_expect_tx(&full_bar[s], (uint32_t)B_BYTES);
-                    tma_load_2d(stage + (DUAL ? 2 : 1) * A_BYTES, &xmap, k0, p0, &full_bar[s]);
+                    // the activation tile: rows p0 .. p0 + box - 1 of the sorted activations, columns
+                    // k0 .. k0+63; rows past the end of the buffer arrive as zeros
+                    const int bi = ncols <= 32 ? 0 : ncols <= 64 ? 1 : ncols <= 128 ? 2 : 3;
+                    mbar_arrive_expect_tx(&full_bar[s], (uint32_t)((32 << bi) * GEMM_BK * 2));
+                    tma_load_2d(stage + (DUAL ? 2 : 1) * A_BYTES, &maps.box[bi], k0, p0, &full_bar[s]);
                 }
                 if (worker) {
                     uint4 a[4];
