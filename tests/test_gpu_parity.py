@@ -477,8 +477,29 @@ def test_moe_forward_host_buffers(zlib, oracle, dev):
     xh = torch.from_numpy(x).pin_memory()
     oh = torch.empty((T, D), dtype=torch.float32).pin_memory()
     layer.forward_host(xh, oh)
-    ref = oracle.moe_ffn(oracle.make_layer(D, F, E, K, types, wg, wu, wd), x, ids_ref, w_ref)
+    Lr = oracle.make_layer(D, F, E, K, types, wg, wu, wd)
+    ref = oracle.moe_ffn(Lr, x, ids_ref, w_ref)
     assert rel_to_norm(oh.numpy(), ref) < REL_TO_NORM
+    first = oh.numpy().copy()
+    # the same pinned buffers again
+    for _ in range(3):
+        oh.zero_()
+        layer.forward_host(xh, oh)
+        assert np.array_equal(oh.numpy().view(np.uint32), first.view(np.uint32))
+    # new contents in the same buffers, another layer on the same context
+    wr2, x2, _, ids2, w2 = routed_inputs(oracle, 23, T, D, E, K)
+    assert wr2.shape == wr.shape
+    layer2 = zlib.Layer(ctx, D, F, E, K, types, to_dev(wg, dev), to_dev(wu, dev), to_dev(wd, dev),
+                        router_w=to_dev(wr2, dev))
+    xh.copy_(torch.from_numpy(x2))
+    for _ in range(3):
+        layer2.forward_host(xh, oh)
+        assert rel_to_norm(oh.numpy(), oracle.moe_ffn(Lr, x2, ids2, w2)) < REL_TO_NORM
+    # pageable buffers
+    xp, op = torch.from_numpy(x.copy()), torch.empty((T, D), dtype=torch.float32)
+    for _ in range(3):
+        layer.forward_host(xp, op)
+        assert np.array_equal(op.numpy().view(np.uint32), first.view(np.uint32))
 
 
 def test_capacity_and_state_errors(zlib, dev):

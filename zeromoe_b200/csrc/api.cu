@@ -91,6 +91,7 @@ struct zmoe_ctx {
     unsigned *ticket = nullptr;
     float *x_stage = nullptr, *out_stage = nullptr;  // device staging of the host entry
     cudaStream_t host_stream = nullptr;
+    int *err_host = nullptr;   // pinned mirror of err: the host entry reads the flag with the same sync as its output
     int routed_t = -1;  // tokens of the current route table
 };
 
@@ -138,6 +139,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     rc |= dev_alloc(&c->x_stage, (size_t)max_tokens * max_d_model);
     rc |= dev_alloc(&c->out_stage, (size_t)max_tokens * max_d_model);
     rc |= ok(cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking));
+    rc |= ok(cudaHostAlloc(reinterpret_cast<void **>(&c->err_host), sizeof(int), cudaHostAllocDefault));
     if (!rc) {
         rc |= ok(cudaMemset(c->err, 0, sizeof(int)));
         rc |= ok(cudaMemset(c->ticket, 0, sizeof(unsigned)));
@@ -171,6 +173,7 @@ void zmoe_ctx_destroy(zmoe_ctx *c) {
     cudaFree(c->x_stage); cudaFree(c->out_stage);
     c->plan.release();
     if (c->host_stream) cudaStreamDestroy(c->host_stream);
+    if (c->err_host) cudaFreeHost(c->err_host);
     delete c;
 }
 
@@ -245,9 +248,9 @@ int zmoe_route(zmoe_layer *L, const float *x_dev, int T, void *stream) {
     a.plan = c->plan.b;
     a.nrt_gu = L->nrt_gu; a.nrt_dn = L->nrt_dn;
     a.ticket = c->ticket;
-    // one CTA per (expert, 4 tokens) re-reads every activation row E times: fine for decode
-    // batches, replaced by a tiled GEMM beyond 64 tokens
-    const bool big = T > 64;
+    // one CTA per (expert, 4 tokens) re-reads every activation row E times: fine up to a few hundred
+    // tokens (the tiled GEMM has only (E / 64) x (T / 64) CTAs: 4 at 128 tokens, 280 us per call)
+    const bool big = T > 256;
     int rc = big ? launch_router_prefill(a, static_cast<cudaStream_t>(stream))
                  : launch_router_decode(a, static_cast<cudaStream_t>(stream));
     g_launches += big ? 4 : 1;
@@ -401,8 +404,13 @@ int zmoe_moe_forward_host(zmoe_layer *L, const float *x_host, float *out_host, i
     int rc = ok(cudaMemcpyAsync(c->x_stage, x_host, n, cudaMemcpyHostToDevice, c->host_stream));
     if (!rc) rc = zmoe_moe_forward(L, c->x_stage, c->out_stage, T, c->host_stream);
     if (!rc) rc = ok(cudaMemcpyAsync(out_host, c->out_stage, n, cudaMemcpyDeviceToHost, c->host_stream));
+    // the device error flag rides on the same stream: one synchronisation for output and status
+    if (!rc) rc = ok(cudaMemcpyAsync(c->err_host, c->err, sizeof(int), cudaMemcpyDeviceToHost, c->host_stream));
     if (!rc) rc = ok(cudaStreamSynchronize(c->host_stream));
-    if (!rc) rc = zmoe_ctx_check(c);
+    if (!rc && *c->err_host) {
+        cudaMemset(c->err, 0, sizeof(int));
+        rc = ZMOE_ERR_DEVICE_WAIT;
+    }
     return rc;
 }
 

@@ -90,6 +90,9 @@ class ExpertShard:
         self.route_ctx.copy_routes(ids, w)
 
         def compute(x_all, ids_local, w_all):
+            # Only 1 / world of the gathered routes name a local expert, which the library cannot see from
+            # the host: choose its kernels by the pairs per expert of the whole batch (the single-GPU rule)
+            self.ctx.set_path(2 if x_all.shape[0] * self.K >= 24 * self.E else 1)
             self.layers[l].set_routes(x_all, ids_local, w_all)
             self.layers[l].expert_ffn(partial)
             return partial
