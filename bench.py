@@ -299,7 +299,7 @@ def main():
     e_lo, e_hi = rank * E // world, (rank + 1) * E // world
     n_local = e_hi - e_lo
     t_all = T * world
-    ctx = lib.Context(max(t_all, 16), D, F, E, K)
+    ctx = lib.Context(max(t_all, 64), D, F, E, K)
     if args.path:
         ctx.set_path(args.path)
     layers, weights = [], []
@@ -467,7 +467,7 @@ def main():
     # ---- the other batch sizes of the sweep --------------------------------------------
     sweep = {}
     if world == 1 and not args.no_sweep:
-        for t2 in (1, 4, 16):
+        for t2 in (1, 4, 16, 64):   # 64: beyond the configuration's sweep, where experts hold several pairs
             if t2 == T:
                 sweep[str(t2)] = {"tokens_per_s": value, "ms_per_step": ms_step}
                 continue

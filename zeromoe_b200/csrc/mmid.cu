@@ -94,12 +94,12 @@ static KernelFn pick_type(int type, int lpr, int upl, bool mma) {
 
 // The multi-token path splits a tile into 16-row pieces and each piece's row into slices of whole
 // half super-blocks, one slice per warp; it needs every output of a tile to find a thread.
-static bool mma_split(int type, const MmidGeom &g, int I, int *ks, int *hpw) {
+static bool mma_split(int type, const MmidGeom &g, int I, bool dual, int *ks, int *hpw) {
     if (type != Q2_K && type != Q3_K && type != Q4_K) return false;
     if (g.R % 16 != 0) return false;
     // rows must start on word boundaries, the same for every lane of a fragment load
     if (((I / QK_K) * block_bytes(type)) % 4 != 0) return false;
-    const int pieces = g.R / 16;
+    const int pieces = (g.R / 16) * (dual ? 2 : 1);   // (piece, matrix) units that need a warp each
     if (pieces > g.ncw || MMID_MAXTOK * g.R > 32 * g.ncw) return false;
     const int nhb = I / 128;
     *ks = 1;   // a power of two
@@ -111,7 +111,7 @@ static bool mma_split(int type, const MmidGeom &g, int I, int *ks, int *hpw) {
 
 int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
     int mma_ks = 0, mma_hpw = 0;
-    const bool mma = L.multi && mma_split(L.type, g, L.I, &mma_ks, &mma_hpw);
+    const bool mma = L.multi && mma_split(L.type, g, L.I, L.dual, &mma_ks, &mma_hpw);
     KernelFn fn = L.dual ? pick_type<true>(L.type, g.lpr, g.upl, mma) : pick_type<false>(L.type, g.lpr, g.upl, mma);
     if (!fn) return ZMOE_ERR_TYPE;
     if ((reinterpret_cast<size_t>(L.w0) & 15) || (L.dual && (reinterpret_cast<size_t>(L.w1) & 15))) return ZMOE_ERR_ALIGN;

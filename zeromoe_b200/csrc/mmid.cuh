@@ -65,7 +65,7 @@ struct MmidParams {
     int nstage;
     int stage_bytes;            // bytes per ring stage (multiple of 128)
     int wtile_bytes;            // bytes reserved per weight tile inside a stage (multiple of 128)
-    int mma_ks_log2;            // multi-token path: log2 of the warps that share one 16-row piece
+    int mma_ks_log2;            // multi-token path: log2 of the warps that share one 16-row piece of one matrix
     int mma_hpw;                // multi-token path: half super-blocks per warp
     int mma_rdiv;               // multi-token path: ceil(65536 / R), for dividing a thread index by R
     int *err;                   // device error flag
@@ -138,8 +138,8 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const __grid_co
     __shared__ StageMeta meta[MMID_MAXSTAGE];
     __shared__ __align__(8) uint64_t iq2_grid[TYPE == IQ2_XXS ? 256 : 1], iq2_sign[TYPE == IQ2_XXS ? 128 : 1];
 
-    // multi-token path: per-warp partial sums [buffer][warp][matrix][16 rows][MAXTOK pairs], double buffered
-    constexpr int PART = 16 * MMID_MAXTOK * (DUAL ? 2 : 1);
+    // multi-token path: per-warp partial sums [buffer][warp][16 rows][MAXTOK pairs], double buffered
+    constexpr int PART = 16 * MMID_MAXTOK;   // one matrix of one warp
     __shared__ __align__(16) float part[MMA ? 2 : 1][MMA ? NCW : 1][MMA ? PART : 1];
     __shared__ __align__(8) uint64_t part_bar;
     __shared__ int s_item_offs[MMID_PLAN_SMEM + 1], s_active[MMID_PLAN_SMEM], s_aoffs[MMID_PLAN_SMEM],
@@ -316,11 +316,13 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const __grid_co
             if (pend_on) {
                 int o_tok, o_row;
                 out_role(o_tok, o_row);
-                const float *pr = &part[q & 1][0][0] + ((o_row >> 4) << p.mma_ks_log2) * PART + (o_row & 15) * MMID_MAXTOK + o_tok;
+                // the piece's warps: ks_n slices of the first matrix, then (DUAL) ks_n of the second
+                const float *pr = &part[q & 1][0][0] + ((o_row >> 4) << (p.mma_ks_log2 + (DUAL ? 1 : 0))) * PART +
+                                  (o_row & 15) * MMID_MAXTOK + o_tok;
                 float a0 = 0.f, a1 = 0.f;
                 for (int i = 0; i < ks_n; ++i) {
                     a0 += pr[i * PART];
-                    if (DUAL) a1 += pr[i * PART + 64];
+                    if (DUAL) a1 += pr[(ks_n + i) * PART];
                 }
                 p.y[pend_idx] = DUAL ? swiglu_f(a0, a1, p.clamp, p.clamp_fused) : a0;
             }
@@ -340,22 +342,19 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const __grid_co
             const uint32_t t1 = stage + p.wtile_bytes + m.w1_off;
             const uint32_t q8base = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
             if (MMA && m_ntok >= 2 && ((t0 | (DUAL ? t1 : 0u)) & (QTraits<TYPE>::kAlign >= 4 ? 3u : 1u)) == 0) {
-                // ---- multi-token item: warp = (16-row piece ti, slice [hb0, hb1) of the row) ----
-                const int ti = warp >> p.mma_ks_log2;
+                // ---- multi-token item: warp = (16-row piece ti, matrix, slice [hb0, hb1) of the row) ----
+                const int wsh = p.mma_ks_log2 + (DUAL ? 1 : 0);
+                const int ti = warp >> wsh, mat = DUAL ? (warp >> p.mma_ks_log2) & 1 : 0;
                 const int hb0 = (warp & (ks_n - 1)) * p.mma_hpw, hb1 = min(hb0 + p.mma_hpw, p.I / 128);
                 // role in the final reduction, read before the stage is released
                 int o_tok, o_row;
                 out_role(o_tok, o_row);
                 const bool o_on = o_tok < m_ntok && o_row < m_nrows;
                 const size_t o_idx = o_on ? (size_t)m.pair[o_tok] * p.ldy + m_r0 + o_row : 0;
-                float f0[4] = {0.f, 0.f, 0.f, 0.f}, f1[4] = {0.f, 0.f, 0.f, 0.f};
-                if (ti * 16 < m_nrows && hb0 < hb1) {
-                    // gate and up one after the other: sharing the activation fragments between them
-                    // costs more registers than the kernel has
-                    mma_rows<TYPE, false>(t0 + (uint32_t)(ti * 16) * p.rbs, 0, p.rbs, q8base, p.q8s, p.I, hb0, hb1, lane, f0, f0);
-                    if (DUAL)
-                        mma_rows<TYPE, false>(t1 + (uint32_t)(ti * 16) * p.rbs, 0, p.rbs, q8base, p.q8s, p.I, hb0, hb1, lane, f1, f1);
-                }
+                float f0[4] = {0.f, 0.f, 0.f, 0.f};
+                if (ti * 16 < m_nrows && hb0 < hb1)
+                    mma_rows<TYPE, false>((mat ? t1 : t0) + (uint32_t)(ti * 16) * p.rbs, 0, p.rbs, q8base, p.q8s, p.I, hb0, hb1,
+                                          lane, f0, f0);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);
                 // the previous multi-token item is finished first: its phase of part_bar must be over
@@ -372,10 +371,6 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const __grid_co
                     if (c < MMID_MAXTOK / 2) {
                         *reinterpret_cast<float2 *>(pw + g * MMID_MAXTOK + 2 * c) = make_float2(f0[0], f0[1]);
                         *reinterpret_cast<float2 *>(pw + (g + 8) * MMID_MAXTOK + 2 * c) = make_float2(f0[2], f0[3]);
-                        if (DUAL) {
-                            *reinterpret_cast<float2 *>(pw + 64 + g * MMID_MAXTOK + 2 * c) = make_float2(f1[0], f1[1]);
-                            *reinterpret_cast<float2 *>(pw + 64 + (g + 8) * MMID_MAXTOK + 2 * c) = make_float2(f1[2], f1[3]);
-                        }
                     }
                 }
                 __syncwarp();
