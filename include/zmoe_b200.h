@@ -172,6 +172,12 @@ int zmoe_route(zmoe_layer *layer, const float *x_dev, int T, void *stream);
  * negative ids are inactive routes */
 int zmoe_set_routes(zmoe_layer *layer, const float *x_dev, const int32_t *ids_dev, const float *weights_dev, int T,
                     void *stream);
+/* the same for a layer that holds the experts [first_expert, first_expert + n_experts) of a larger
+ * model (one rank of an expert-parallel group): ids are the model's expert numbers, the ones outside
+ * the layer's window become inactive routes.  Same convention as the reference's hot / cold branch
+ * route_map (backends/ggml/moe_partial_route_ggml.hpp:13-35): an expert owned elsewhere maps to -1. */
+int zmoe_set_routes_window(zmoe_layer *layer, const float *x_dev, const int32_t *ids_dev, const float *weights_dev,
+                           int T, int first_expert, void *stream);
 /* expert FFN + combine over the current routes: out_dev [T, d_model] is
  * overwritten (accumulate = 0) or added to (accumulate = 1) */
 int zmoe_expert_ffn(zmoe_layer *layer, float *out_dev, int T, int accumulate, void *stream);

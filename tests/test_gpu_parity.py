@@ -424,6 +424,37 @@ def test_moe_layer_supplied_routes_with_inactive_ids(zlib, oracle, dev, T):
         ctx.set_path(0)
 
 
+def test_routes_of_a_window_of_experts(zlib, dev):
+    """zmoe_set_routes_window: model-wide expert ids on a layer that holds experts [first, first + E)"""
+    import torch
+    D, F, E, K, T = 1024, 512, 6, 4, 9
+    first, total = 10, 24
+    types = (synth.Q2_K, synth.Q2_K, synth.Q3_K)
+    rng = synth.rng_for(31, 0)
+    wg = to_dev(synth.expert_weights(types[0], E, F, D, rng), dev)
+    wu = to_dev(synth.expert_weights(types[1], E, F, D, rng), dev)
+    wd = to_dev(synth.expert_weights(types[2], E, D, F, rng), dev)
+    x = to_dev(synth.activations(T, D, rng), dev)
+    ids = np.stack([rng.permutation(total)[:K] for _ in range(T)]).astype(np.int32)
+    ids[1, 0] = -1                                       # an inactive route stays inactive
+    wts = to_dev(rng.uniform(0.05, 0.3, size=(T, K)).astype(np.float32), dev)
+    local = np.where((ids >= first) & (ids < first + E), ids - first, -1).astype(np.int32)
+    assert (local >= 0).sum() > 4
+    ctx = zlib.Context(16, D, F, E, K)
+    layer = zlib.Layer(ctx, D, F, E, K, types, wg, wu, wd)
+    layer.set_routes(x, to_dev(local, dev), wts)
+    a = torch.full((T, D), float("nan"), device=dev)
+    layer.expert_ffn(a)
+    layer.set_routes_window(x, to_dev(ids, dev), wts, first)
+    b = torch.full((T, D), float("nan"), device=dev)
+    layer.expert_ffn(b)
+    _sync()
+    ctx.check()
+    got_ids, _ = ctx.routes(T, K)
+    assert np.array_equal(got_ids, local)
+    assert torch.equal(a, b)
+
+
 def test_deepseek_shaped_layer_with_shared_expert(zlib, oracle, dev):
     """fourth benchmark configuration, scaled down in expert count only: hidden 7168, ffn 2048,
     sigmoid gating, 8 groups with the top 4 kept, top-8, normalised weights, Q4_K, one shared expert"""

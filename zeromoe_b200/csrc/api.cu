@@ -263,14 +263,15 @@ int zmoe_route(zmoe_layer *L, const float *x_dev, int T, void *stream) {
     return rc;
 }
 
-int zmoe_set_routes(zmoe_layer *L, const float *x_dev, const int32_t *ids_dev, const float *weights_dev, int T,
-                    void *stream) {
+static int set_routes_impl(zmoe_layer *L, const float *x_dev, const int32_t *ids_dev, const float *weights_dev, int T,
+                           int first_expert, bool window, void *stream) {
     if (!L || !x_dev || !ids_dev || !weights_dev || T <= 0) return ZMOE_ERR_ARG;
     zmoe_ctx *c = L->ctx;
     if (T > c->max_t) return ZMOE_ERR_CAPACITY;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t P = (size_t)T * L->d.topk;
-    int rc = ok(cudaMemcpyAsync(c->ids, ids_dev, P * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
+    int rc = window ? launch_window_ids(ids_dev, c->ids, (int)P, first_expert, L->d.n_experts, st)
+                    : ok(cudaMemcpyAsync(c->ids, ids_dev, P * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
     if (!rc) rc = ok(cudaMemcpyAsync(c->weights, weights_dev, P * sizeof(float), cudaMemcpyDeviceToDevice, st));
     if (!rc) rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x, T, L->d.d_model, q8_layout_of(L->d.gate.type), st);
     if (!rc && q8_layout_of(L->d.up.type) != q8_layout_of(L->d.gate.type)) {
@@ -278,8 +279,19 @@ int zmoe_set_routes(zmoe_layer *L, const float *x_dev, const int32_t *ids_dev, c
         g_launches += 1;
     }
     if (!rc) rc = launch_plan_from_ids(c->ids, (int)P, L->d.n_experts, c->plan.b, L->nrt_gu, L->nrt_dn, st);
-    if (!rc) { g_launches += 2; c->routed_t = T; c->x_last = x_dev; }
+    if (!rc) { g_launches += window ? 3 : 2; c->routed_t = T; c->x_last = x_dev; }
     return rc;
+}
+
+int zmoe_set_routes(zmoe_layer *L, const float *x_dev, const int32_t *ids_dev, const float *weights_dev, int T,
+                    void *stream) {
+    return set_routes_impl(L, x_dev, ids_dev, weights_dev, T, 0, false, stream);
+}
+
+int zmoe_set_routes_window(zmoe_layer *L, const float *x_dev, const int32_t *ids_dev, const float *weights_dev, int T,
+                           int first_expert, void *stream) {
+    if (first_expert < 0) return ZMOE_ERR_ARG;
+    return set_routes_impl(L, x_dev, ids_dev, weights_dev, T, first_expert, true, stream);
 }
 
 int zmoe_expert_ffn(zmoe_layer *L, float *out_dev, int T, int accumulate, void *stream) {

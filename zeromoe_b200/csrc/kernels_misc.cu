@@ -209,6 +209,22 @@ int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &pl
                : ZMOE_ERR_CUDA;
 }
 
+__global__ void window_ids_kernel(const int32_t *in, int32_t *out, int n_ids, int first, int n) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_ids; i += gridDim.x * blockDim.x) {
+        const int e = in[i];
+        out[i] = (e >= first && e < first + n) ? e - first : -1;
+    }
+}
+
+int launch_window_ids(const int32_t *in, int32_t *out, int n_ids, int first, int n, cudaStream_t st) {
+    const int grid = (n_ids + 255) / 256 < 148 ? (n_ids + 255) / 256 : 148;
+    return launch_pdl(window_ids_kernel, dim3(grid > 0 ? grid : 1), dim3(256), 0, st, in, out, n_ids, first, n) == cudaSuccess
+               ? ZMOE_OK
+               : ZMOE_ERR_CUDA;
+}
+
 // dense matmul as a one-expert plan: every row of x is a pair of expert 0
 __global__ void plan_dense_kernel(int S, PlanOut po) {
     pdl_wait_prior_grid();

@@ -27,11 +27,12 @@ def localise_ids(ids_all, e_lo, e_hi):
     return torch.where(owned, ids_all - e_lo, torch.full_like(ids_all, -1))
 
 
-def exchange_forward(x, ids, weights, e_lo, e_hi, compute, group=None):
+def exchange_forward(x, ids, weights, e_lo, e_hi, compute, group=None, out=None, localise=True):
     """x [T, D], ids [T, K] int32 (global), weights [T, K] -> out [T, D].
 
-    compute(x_all [N*T, D], ids_local [N*T, K], w_all [N*T, K]) -> partial [N*T, D] sums the
-    local experts' contributions for every token of every rank."""
+    compute(x_all [N*T, D], ids [N*T, K], w_all [N*T, K]) -> partial [N*T, D] sums the local experts'
+    contributions for every token of every rank.  It is handed ids inside this rank's shard (-1 for experts
+    owned elsewhere), or with localise=False the gathered global ids (a backend that maps them itself)."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     T = x.shape[0]
@@ -41,8 +42,9 @@ def exchange_forward(x, ids, weights, e_lo, e_hi, compute, group=None):
     dist.all_gather_into_tensor(x_all, x.contiguous(), group=group)
     dist.all_gather_into_tensor(ids_all, ids.contiguous(), group=group)
     dist.all_gather_into_tensor(w_all, weights.contiguous(), group=group)
-    partial = compute(x_all, localise_ids(ids_all, e_lo, e_hi), w_all)
-    out = torch.empty_like(x)
+    partial = compute(x_all, localise_ids(ids_all, e_lo, e_hi) if localise else ids_all, w_all)
+    if out is None:
+        out = torch.empty_like(x)
     if dist.get_backend(group) == "gloo":       # gloo has no reduce-scatter: reduce, then take this rank's rows
         dist.all_reduce(partial, group=group)
         out.copy_(partial[rank * T:(rank + 1) * T])
@@ -89,14 +91,19 @@ class ExpertShard:
         self.routers[l].route(x)
         self.route_ctx.copy_routes(ids, w)
 
-        def compute(x_all, ids_local, w_all):
+        def compute(x_all, ids_all, w_all):
             # Only 1 / world of the gathered routes name a local expert, which the library cannot see from
             # the host: choose its kernels by the pairs per expert of the whole batch (the single-GPU rule)
             self.ctx.set_path(2 if x_all.shape[0] * self.K >= 24 * self.E else 1)
-            self.layers[l].set_routes(x_all, ids_local, w_all)
+            # the library maps the model-wide ids into this rank's window (one kernel)
+            self.layers[l].set_routes_window(x_all, ids_all, w_all, self.e_lo)
             self.layers[l].expert_ffn(partial)
             return partial
-        out.copy_(exchange_forward(x, ids, w, self.e_lo, self.e_hi, compute))
+        # the reduce-scatter writes straight into the caller's rows
+        if out.is_contiguous():
+            exchange_forward(x, ids, w, self.e_lo, self.e_hi, compute, out=out, localise=False)
+        else:
+            out.copy_(exchange_forward(x, ids, w, self.e_lo, self.e_hi, compute, localise=False))
 
 
 def _router_only(lib, ctx, d_model, d_ff, n_experts, topk, types, wg, wu, wd, wr):
