@@ -302,6 +302,9 @@ int launch_q8rows_to_blocks(const uint8_t *q8, uint8_t *blocks, int rows, int I,
 // Pairs with a negative id contribute a zero row, ids >= E a NaN row
 // (reference kernels/quant/kquant_matmul.cu:659-662).
 // ------------------------------------------------------------------------
+// KMAX: routes per token whose rows are fetched before any is added (one trip to L2 instead of K in a
+// row); 0: any K, row by row.
+template <int KMAX>
 __global__ void __launch_bounds__(256) combine_kernel(float *out, const float *y, const float *w, const int32_t *ids,
                                                       int T, int K, int D, int E, int accumulate) {
     pdl_wait_prior_grid();
@@ -310,16 +313,28 @@ __global__ void __launch_bounds__(256) combine_kernel(float *out, const float *y
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < (long)T * D4; i += (long)gridDim.x * blockDim.x) {
         const int t = (int)(i / D4), d4 = (int)(i % D4);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int k = 0; k < K; ++k) {
+        auto row = [&](int k) -> float4 {
             const int id = ids[t * K + k];
-            const float wk = w[t * K + k];
-            float4 v;
-            if (id < 0) v = make_float4(0.f, 0.f, 0.f, 0.f);
-            else if (id >= E) v = make_float4(nanf(""), nanf(""), nanf(""), nanf(""));
-            else v = reinterpret_cast<const float4 *>(y + ((size_t)t * K + k) * D)[d4];
+            if (id < 0) return make_float4(0.f, 0.f, 0.f, 0.f);
+            if (id >= E) return make_float4(nanf(""), nanf(""), nanf(""), nanf(""));
+            return reinterpret_cast<const float4 *>(y + ((size_t)t * K + k) * D)[d4];
+        };
+        auto add = [&](int k, float4 v, float wk) {
             const float4 pr = make_float4(__fmul_rn(wk, v.x), __fmul_rn(wk, v.y), __fmul_rn(wk, v.z), __fmul_rn(wk, v.w));
             if (k == 0) acc = pr;
             else acc = make_float4(__fadd_rn(acc.x, pr.x), __fadd_rn(acc.y, pr.y), __fadd_rn(acc.z, pr.z), __fadd_rn(acc.w, pr.w));
+        };
+        if (KMAX > 0) {
+            float4 v[KMAX > 0 ? KMAX : 1];
+            float wk[KMAX > 0 ? KMAX : 1];
+#pragma unroll
+            for (int k = 0; k < KMAX; ++k)
+                if (k < K) { v[k] = row(k); wk[k] = w[t * K + k]; }
+#pragma unroll
+            for (int k = 0; k < KMAX; ++k)
+                if (k < K) add(k, v[k], wk[k]);
+        } else {
+            for (int k = 0; k < K; ++k) add(k, row(k), w[t * K + k]);
         }
         float4 *o = reinterpret_cast<float4 *>(out + (size_t)t * D) + d4;
         if (accumulate) {
@@ -333,10 +348,13 @@ __global__ void __launch_bounds__(256) combine_kernel(float *out, const float *y
 int launch_combine(float *out, const float *y, const float *w, const int32_t *ids, int T, int K, int D, int E,
                    int accumulate, cudaStream_t st) {
     const long n = (long)T * (D / 4);
+    // one float4 per thread where that still fills the machine: a short batch is bound by the trip to L2
     long grid = (n + 255) / 256;
+    int threads = 256;
+    if (grid < 148) { threads = 64; grid = (n + 63) / 64; }
     if (grid > 148 * 8) grid = 148 * 8;
-    return launch_pdl(combine_kernel, dim3((unsigned)grid), dim3(256), 0, st, out, y, w, ids, T, K, D, E, accumulate) ==
-                   cudaSuccess
+    auto fn = K <= 8 ? combine_kernel<8> : K <= 16 ? combine_kernel<16> : combine_kernel<0>;
+    return launch_pdl(fn, dim3((unsigned)grid), dim3(threads), 0, st, out, y, w, ids, T, K, D, E, accumulate) == cudaSuccess
                ? ZMOE_OK
                : ZMOE_ERR_CUDA;
 }
