@@ -112,6 +112,10 @@ __device__ void route_token_warp(const RouterSpec &sp, const float *row_in, floa
         __syncwarp();
     }
     float sum_w = 0.f;
+    // lane k keeps the weight of route k: the normalisation below then needs no trip back to the
+    // memory the weights were just stored to (K <= 32; more routes take the in-place path)
+    float mine = 0.f;
+    const bool in_regs = K <= 32;
     for (int k = 0; k < K; ++k) {
         float bv = -CUDART_INF_F;
         int bi = 0x7fffffff;
@@ -125,13 +129,18 @@ __device__ void route_token_warp(const RouterSpec &sp, const float *row_in, floa
         const float w = prob_s[bi];
         if (lane == 0) {
             ids[k] = bi;
-            weights[k] = w;
+            if (!in_regs) weights[k] = w;
             sel_s[bi] = CUDART_NAN_F;  // taken
         }
+        if (lane == k) mine = w;
         sum_w += w;
         __syncwarp();
     }
-    if (lane == 0) {
+    if (in_regs) {
+        if (sp.normalize) mine *= 1.0f / fmaxf(sum_w, 6.103515625e-5f);
+        if (sp.weight_scale != 0.0f) mine *= sp.weight_scale;
+        if (lane < K) weights[lane] = mine;
+    } else if (lane == 0) {
         if (sp.normalize) {
             const float inv = 1.0f / fmaxf(sum_w, 6.103515625e-5f);
             for (int k = 0; k < K; ++k) weights[k] *= inv;
