@@ -135,14 +135,14 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     rc |= dev_alloc(&c->weights, P);
     rc |= c->plan.alloc(max_experts, (int)P);
     rc |= dev_alloc(&c->err, 1);
-    rc |= dev_alloc(&c->ticket, 1);
+    rc |= dev_alloc(&c->ticket, 1 + ROUTER_MAX_GROUPS);
     rc |= dev_alloc(&c->x_stage, (size_t)max_tokens * max_d_model);
     rc |= dev_alloc(&c->out_stage, (size_t)max_tokens * max_d_model);
     rc |= ok(cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking));
     rc |= ok(cudaHostAlloc(reinterpret_cast<void **>(&c->err_host), sizeof(int), cudaHostAllocDefault));
     if (!rc) {
         rc |= ok(cudaMemset(c->err, 0, sizeof(int)));
-        rc |= ok(cudaMemset(c->ticket, 0, sizeof(unsigned)));
+        rc |= ok(cudaMemset(c->ticket, 0, (1 + ROUTER_MAX_GROUPS) * sizeof(unsigned)));
         rc |= ok(cudaMemset(c->plan.b.hdr, 0, 4 * sizeof(int)));
         rc |= ok(cudaMemset(c->zero_ids, 0, (size_t)max_tokens * sizeof(int32_t)));
         // 1.0f = 0x3f800000: fill through a host staging vector (done once)

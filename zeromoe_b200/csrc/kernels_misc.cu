@@ -15,6 +15,7 @@ namespace zmoe {
 // routes all tokens and builds the plan.
 // ------------------------------------------------------------------------
 constexpr int ROUTER_TPB = 4;      // tokens per CTA
+static_assert(ROUTER_TPB * ROUTER_MAX_GROUPS >= 256, "the decode router serves batches of up to 256 tokens");
 constexpr int ROUTER_THREADS = 256;
 constexpr int ROUTER_MAXV = 8;     // float4 per thread: rows up to 8192 elements
 constexpr int ROUTER_IDS_SMEM = 2048;  // pairs whose ids the planner mirrors in shared memory
@@ -78,11 +79,13 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const Rou
         const int t = idx / nb, b = idx % nb;
         quantize_block_q8k(a.x + (size_t)t * a.D + QK_K * b, a.q8x + (size_t)t * stride, a.D, b, lane, a.q8_layout);
     }
+    // Two levels of tickets: the last of the E CTAs of a token group routes that group's tokens (one warp per
+    // token) while other groups are still computing logits; the last group to finish builds the plan.
     __threadfence();
     __syncthreads();
-    if (tid == 0) s_ticket = atomicAdd(a.ticket, 1u);
+    if (tid == 0) s_ticket = atomicAdd(&a.ticket[1 + tg], 1u);
     __syncthreads();
-    if (s_ticket != gridDim.x - 1) return;
+    if (s_ticket != (unsigned)a.E - 1) return;
     __threadfence();
 
     float *prob_s = reinterpret_cast<float *>(dyn) + (size_t)warp * 2 * a.E;
@@ -91,18 +94,28 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const Rou
     int *pre_s = cnt_s + a.E + 1;
     int *ids_s = a.T * a.K <= ROUTER_IDS_SMEM ? pre_s + a.E + 1 : nullptr;
     RouterSpec sp{a.E, a.K, a.gating, a.normalize, a.weight_scale, a.n_groups, a.n_groups_used};
-    for (int t = warp; t < a.T; t += NW)
+    for (int t = t0 + warp; t < a.T && t < t0 + ROUTER_TPB; t += NW)
         route_token_warp(sp, a.logits + (size_t)t * a.E, a.logits + (size_t)t * a.E, a.bias,
                          a.ids + (size_t)t * a.K, a.weights + (size_t)t * a.K, prob_s, sel_s, lane);
+    __threadfence();
     __syncthreads();
+    const unsigned n_tg = (unsigned)((a.T + ROUTER_TPB - 1) / ROUTER_TPB);
+    if (tid == 0) {
+        a.ticket[1 + tg] = 0u;
+        s_ticket = atomicAdd(&a.ticket[0], 1u);
+    }
+    __syncthreads();
+    if (s_ticket != n_tg - 1) return;
+    __threadfence();
     PlanOut po{a.plan.hdr, a.plan.active, a.plan.offs, a.plan.slot, a.plan.item_offs_gu, a.plan.item_offs_dn,
                a.plan.freq, a.plan.aoffs, a.plan.antok, a.nrt_gu, a.nrt_dn};
     build_plan_cta(a.ids, a.T * a.K, a.E, po, cnt_s, pre_s, ids_s);
-    if (tid == 0) *a.ticket = 0u;
+    if (tid == 0) a.ticket[0] = 0u;
 }
 
 int launch_router_decode(const RouterArgs &a, cudaStream_t st) {
     if (a.D / 4 > ROUTER_MAXV * ROUTER_THREADS) return ZMOE_ERR_SHAPE;
+    if ((a.T + ROUTER_TPB - 1) / ROUTER_TPB > ROUTER_MAX_GROUPS) return ZMOE_ERR_CAPACITY;
     const size_t smem = (size_t)2 * (ROUTER_THREADS / 32) * a.E * sizeof(float) + (size_t)2 * (a.E + 1) * sizeof(int) +
                         (a.T * a.K <= ROUTER_IDS_SMEM ? (size_t)a.T * a.K * sizeof(int) : 0);
     if (smem > 200 * 1024) return ZMOE_ERR_SHAPE;

@@ -20,6 +20,8 @@ struct PlanBuffers {
     int cap_e = 0;
 };
 
+constexpr int ROUTER_MAX_GROUPS = 64;   // token groups (of 4) the decode router can ticket: 256 tokens
+
 struct RouterArgs {
     const float *x;        // [T, D]
     const float *wr;       // [E, D]
@@ -35,7 +37,7 @@ struct RouterArgs {
     int q8_layout;         // unit layout of q8x (that of the gate / up weight format)
     PlanBuffers plan;
     int nrt_gu, nrt_dn;
-    unsigned *ticket;      // zero-initialised counter, left at zero
+    unsigned *ticket;      // 1 + ROUTER_MAX_GROUPS zero-initialised counters, left at zero
 };
 
 // geometry of one mmid launch, fixed per (type, I, O)
