@@ -270,16 +270,16 @@ static int set_routes_impl(zmoe_layer *L, const float *x_dev, const int32_t *ids
     if (T > c->max_t) return ZMOE_ERR_CAPACITY;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t P = (size_t)T * L->d.topk;
-    int rc = window ? launch_window_ids(ids_dev, c->ids, (int)P, first_expert, L->d.n_experts, st)
-                    : ok(cudaMemcpyAsync(c->ids, ids_dev, P * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
-    if (!rc) rc = ok(cudaMemcpyAsync(c->weights, weights_dev, P * sizeof(float), cudaMemcpyDeviceToDevice, st));
-    if (!rc) rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x, T, L->d.d_model, q8_layout_of(L->d.gate.type), st);
+    int rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x, T, L->d.d_model, q8_layout_of(L->d.gate.type), st);
     if (!rc && q8_layout_of(L->d.up.type) != q8_layout_of(L->d.gate.type)) {
         rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x2, T, L->d.d_model, q8_layout_of(L->d.up.type), st);
         g_launches += 1;
     }
-    if (!rc) rc = launch_plan_from_ids(c->ids, (int)P, L->d.n_experts, c->plan.b, L->nrt_gu, L->nrt_dn, st);
-    if (!rc) { g_launches += window ? 3 : 2; c->routed_t = T; c->x_last = x_dev; }
+    // the planner takes the routes in (copy, window mapping) before it groups them: one launch
+    if (!rc)
+        rc = launch_plan_ingest(ids_dev, weights_dev, c->ids, c->weights, (int)P, L->d.n_experts, first_expert, window,
+                                c->plan.b, L->nrt_gu, L->nrt_dn, st);
+    if (!rc) { g_launches += 2; c->routed_t = T; c->x_last = x_dev; }
     return rc;
 }
 

@@ -204,38 +204,53 @@ int launch_router_prefill(const RouterArgs &a, cudaStream_t st) {
 // ------------------------------------------------------------------------
 // stand-alone planners
 // ------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) plan_from_ids_kernel(const int32_t *ids, int P, int E, PlanOut po) {
+// Routes that come from outside (src_ids / src_w, optional) are first copied into the context's own
+// tables, expert numbers outside the window [first, first + E) becoming -1 (negative ones stay as they are).
+struct RouteIngest {
+    const int32_t *src_ids = nullptr;
+    const float *src_w = nullptr;
+    int32_t *dst_ids = nullptr;
+    float *dst_w = nullptr;
+    int first = 0;
+    int window = 0;      // 0: ids are copied unchanged
+};
+
+__global__ void __launch_bounds__(1024) plan_from_ids_kernel(const int32_t *ids, int P, int E, PlanOut po, RouteIngest in) {
     extern __shared__ int plan_s[];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
+    if (in.src_ids) {
+        for (int p = threadIdx.x; p < P; p += blockDim.x) {
+            const int e = in.src_ids[p];
+            in.dst_ids[p] = !in.window ? e : (e >= in.first && e < in.first + E) ? e - in.first : -1;
+            in.dst_w[p] = in.src_w[p];
+        }
+        __syncthreads();
+    }
     build_plan_cta(ids, P, E, po, plan_s, plan_s + E + 1, P <= ROUTER_IDS_SMEM ? plan_s + 2 * (E + 1) : nullptr);
 }
 
-int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
-                         cudaStream_t st) {
+static int launch_plan(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
+                       const RouteIngest &in, cudaStream_t st) {
     PlanOut po{plan.hdr, plan.active, plan.offs, plan.slot, plan.item_offs_gu, plan.item_offs_dn, plan.freq,
                plan.aoffs, plan.antok, nrt_gu, nrt_dn};
     const size_t smem = (size_t)2 * (E + 1) * sizeof(int) + (P <= ROUTER_IDS_SMEM ? (size_t)P * sizeof(int) : 0);
     if (smem > 48 * 1024) return ZMOE_ERR_SHAPE;
-    return launch_pdl(plan_from_ids_kernel, dim3(1), dim3(1024), smem, st, ids, P, E, po) == cudaSuccess
+    return launch_pdl(plan_from_ids_kernel, dim3(1), dim3(1024), smem, st, ids, P, E, po, in) == cudaSuccess
                ? ZMOE_OK
                : ZMOE_ERR_CUDA;
 }
 
-__global__ void window_ids_kernel(const int32_t *in, int32_t *out, int n_ids, int first, int n) {
-    pdl_wait_prior_grid();
-    pdl_launch_dependents();
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_ids; i += gridDim.x * blockDim.x) {
-        const int e = in[i];
-        out[i] = (e >= first && e < first + n) ? e - first : -1;
-    }
+int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
+                         cudaStream_t st) {
+    return launch_plan(ids, P, E, plan, nrt_gu, nrt_dn, RouteIngest(), st);
 }
 
-int launch_window_ids(const int32_t *in, int32_t *out, int n_ids, int first, int n, cudaStream_t st) {
-    const int grid = (n_ids + 255) / 256 < 148 ? (n_ids + 255) / 256 : 148;
-    return launch_pdl(window_ids_kernel, dim3(grid > 0 ? grid : 1), dim3(256), 0, st, in, out, n_ids, first, n) == cudaSuccess
-               ? ZMOE_OK
-               : ZMOE_ERR_CUDA;
+int launch_plan_ingest(const int32_t *src_ids, const float *src_w, int32_t *ids, float *w, int P, int E, int first,
+                       bool window, const PlanBuffers &plan, int nrt_gu, int nrt_dn, cudaStream_t st) {
+    RouteIngest in;
+    in.src_ids = src_ids; in.src_w = src_w; in.dst_ids = ids; in.dst_w = w; in.first = first; in.window = window ? 1 : 0;
+    return launch_plan(ids, P, E, plan, nrt_gu, nrt_dn, in, st);
 }
 
 // dense matmul as a one-expert plan: every row of x is a pair of expert 0

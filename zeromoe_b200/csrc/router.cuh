@@ -218,13 +218,27 @@ __device__ void build_plan_cta(const int32_t *ids, int P, int E, const PlanOut &
     }
     __syncthreads();
     if (P <= 8192) {
-        // stable fill: thread e walks the pairs in order
+        // Stable fill by one warp, 32 pairs at a time: lanes that name the same expert find each other
+        // (match), the first of them takes the expert's cursor and moves it on, each writes its pair at
+        // cursor + its rank among them.  (A thread per expert walking all pairs costs P dependent steps:
+        // 44 us at 1024 pairs.)
         const int *src = ids_s ? ids_s : ids;
-        for (int e = tid; e < E; e += nt) {
-            if (cnt_s[e] == 0) continue;
-            int w = pre_s[e];
-            for (int p = 0; p < P; ++p)
-                if (src[p] == e) po.slot[w++] = p;
+        if (tid < 32) {
+            for (int p0 = 0; p0 < P; p0 += 32) {
+                const int p = p0 + lane;
+                const int e = p < P ? src[p] : -1;
+                const bool on = e >= 0 && e < E;
+                const unsigned peers = __match_any_sync(0xffffffffu, on ? e : -1 - lane);
+                const int leader = __ffs(peers) - 1;
+                int base = 0;
+                if (on && lane == leader) {
+                    base = pre_s[e];
+                    pre_s[e] = base + __popc(peers);
+                }
+                base = __shfl_sync(0xffffffffu, base, leader);
+                if (on) po.slot[base + __popc(peers & ((1u << lane) - 1u))] = p;
+                __syncwarp();
+            }
         }
     } else {
         for (int p = tid; p < P; p += nt) {

@@ -100,8 +100,10 @@ int launch_q8_roundtrip_f16(const float *x, int ldx, void *out_f16, float *scale
 
 int launch_router_decode(const RouterArgs &a, cudaStream_t st);
 int launch_router_prefill(const RouterArgs &a, cudaStream_t st);  // four launches; for large T
-// ids of a model-wide numbering -> ids inside the window [first, first + n), -1 outside (negative stay negative)
-int launch_window_ids(const int32_t *in, int32_t *out, int n_ids, int first, int n, cudaStream_t st);
+// the planner, first copying routes from outside into the context's tables (ids, w); window: expert numbers
+// outside [first, first + E) become -1
+int launch_plan_ingest(const int32_t *src_ids, const float *src_w, int32_t *ids, float *w, int P, int E, int first,
+                       bool window, const PlanBuffers &plan, int nrt_gu, int nrt_dn, cudaStream_t st);
 int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
                          cudaStream_t st);
 int launch_plan_dense(int S, const PlanBuffers &plan, int nrt, cudaStream_t st);
