@@ -155,20 +155,32 @@ class ClockSampler:
         self.rows = []
         self.proc = None
         self.idx = gpu_index
+        self.t0 = self.t1 = None
+
+    def mark(self, begin):
+        """the timed region begins / ends now: only samples taken inside it count"""
+        if begin:
+            self.t0 = time.perf_counter()
+        else:
+            self.t1 = time.perf_counter()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            # nvidia-smi needs a moment to come up: wait for its first line so that the timed region is covered
+            deadline = time.perf_counter() + 2.0
+            while not self.rows and time.perf_counter() < deadline:
+                time.sleep(0.01)
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([time.perf_counter()] + [c.strip() for c in line.split(",")])
 
     def stop(self):
         if not self.proc:
@@ -181,7 +193,11 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        rows = [r[1:] for r in self.rows
+                if self.t0 is None or self.t1 is None or self.t0 <= r[0] <= self.t1 + 0.03]
+        if not rows:                       # region shorter than one sampling period: the nearest samples
+            rows = [r[1:] for r in self.rows]
+        for r in rows:
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
@@ -254,7 +270,7 @@ def run_reference_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--tokens", type=int, default=16, help="tokens per step per GPU (1, 4 or 16 in the sweep)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -373,7 +389,10 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.mark(True)
     ms_step = timed(step, args.steps)
+    if rank == 0:
+        sampler.mark(False)
     clocks = sampler.stop() if rank == 0 else None
     launches = launches_per_step * args.steps
     ctx.check()
