@@ -30,7 +30,7 @@ def _inputs():
     return wg, wu, wd, xs, ids, ws
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, results, own_mapping=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -43,18 +43,29 @@ def _worker(rank, world, port, results):
 
     def compute(x_all, ids_local, w_all):
         return torch.from_numpy(O.moe_ffn(L, x_all.numpy(), ids_local.numpy(), w_all.numpy()))
-    out = ep.exchange_forward(torch.from_numpy(xs[rank]), torch.from_numpy(ids[rank]), torch.from_numpy(ws[rank]),
-                              e_lo, e_hi, compute)
+    if own_mapping:
+        # the backend maps model-wide ids into its window itself (what zmoe_set_routes_window does on the GPU)
+        # and the result lands in the caller's tensor
+        def compute_global(x_all, ids_all, w_all):
+            return compute(x_all, ep.localise_ids(ids_all, e_lo, e_hi), w_all)
+        out = torch.full((T, D), float("nan"))
+        ret = ep.exchange_forward(torch.from_numpy(xs[rank]), torch.from_numpy(ids[rank]), torch.from_numpy(ws[rank]),
+                                  e_lo, e_hi, compute_global, out=out, localise=False)
+        assert ret is out
+    else:
+        out = ep.exchange_forward(torch.from_numpy(xs[rank]), torch.from_numpy(ids[rank]), torch.from_numpy(ws[rank]),
+                                  e_lo, e_hi, compute)
     results[rank] = out.numpy()
     dist.destroy_process_group()
 
 
-def test_two_rank_exchange_matches_single_rank(oracle):
+@pytest.mark.parametrize("own_mapping", [False, True])
+def test_two_rank_exchange_matches_single_rank(oracle, own_mapping):
     world = 2
-    port = 29000 + os.getpid() % 2000
+    port = 29000 + (os.getpid() + 7 * own_mapping) % 2000
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, results, own_mapping), nprocs=world, join=True)
     wg, wu, wd, xs, ids, ws = _inputs()
     L = oracle.make_layer(D, F, E, K, TYPES, wg, wu, wd)
     for r in range(world):
