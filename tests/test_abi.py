@@ -33,6 +33,9 @@ def test_argument_validation_needs_no_device():
     assert L.zmoe_layer_create(None, None, C.byref(h)) == -1
     assert L.zmoe_route(None, None, 1, None) == -1
     assert L.zmoe_expert_ffn(None, None, 1, 0, None) == -1
+    assert L.zmoe_set_routes(None, None, None, None, 1, None) == -1
+    assert L.zmoe_set_routes_window(None, None, None, None, 1, 0, None) == -1
+    assert L.zmoe_ctx_set_path(None, 0) == -1
     assert L.zmoe_quantize_q8_K(None, None, 1, 256, lib.Q4_K, None) == -1
     assert L.zmoe_block_isums(99, None, None, None, None, 1, 256, None) == -1
     assert L.zmoe_reserve(4, 100) == -1
