@@ -10,11 +10,15 @@
 //     pairs routed to that expert).  Rows of one expert are contiguous, so a
 //     tile is ONE contiguous byte range.
 //   * a producer warp streams items through an NSTAGE ring in shared memory
-//     with 1-D bulk asynchronous copies (TMA engine), completion on mbarriers;
-//     the packed Q8_K rows of the item's pairs ride in the same stage.
-//   * consumer warps decode from shared memory.  A row is split over LPR lanes,
-//     each lane owns UPL "units" (64 elements) whose activation words stay in
-//     registers across rows; dot products are dp4a, reduced by warp shuffles.
+//     with asynchronous copies on the TMA engine, completion on mbarriers: a
+//     1-D bulk copy of the tile, or -- where the launch has a tiled map of the
+//     tensor -- one tiled copy whose box is 16 bytes wider than a row, which pads
+//     the rows in shared memory (bank-conflict-free fragment loads).  The packed
+//     Q8_K rows of the item's pairs ride in the same stage.
+//   * consumer warps decode from shared memory.  One pair: a row is split over
+//     LPR lanes, each lane owns UPL "units" (64 elements) whose activation words
+//     stay in registers across rows; dot products are dp4a, reduced by warp
+//     shuffles.  Two to four pairs (MMA instantiations): mmid_mma.cuh.
 //   * DUAL mode reads a gate tile and an up tile and writes SwiGLU(gate, up)
 //     (reference kernels/math/expert_activation.cu:31-59).
 // Every wait is bounded; on expiry the CTA raises an error flag and unwinds.
