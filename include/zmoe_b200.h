@@ -8,10 +8,19 @@
  * Functions that return int return 0 on success and a negative ZMOE_ERR_* code
  * otherwise; there is no CPU fallback anywhere in the library.
  *
- * Numerics: activations are quantised to Q8_K per 256 values and multiplied in
- * integer arithmetic, as the reference's CPU path (ggml MUL_MAT_ID) does; the
- * per-super-block int32 sums are exact, f32 assembly differs only in summation
- * order.
+ * Numerics.  Activations are quantised to Q8_K per 256 values, as the reference's
+ * CPU path (ggml MUL_MAT_ID) does.  Two families of kernels multiply them:
+ *   - the decode kernels (every launch_*_matmul symbol, the op hook, and the layer
+ *     entry below zmoe_gemm_min_pairs_per_expert() pairs per expert) work in integer
+ *     arithmetic: the per-super-block int32 sums are exact, the f32 assembly differs
+ *     from the CPU path only in summation order;
+ *   - the tensor-core grouped GEMM (the layer entry from that threshold up, or
+ *     zmoe_ctx_set_path(ctx, 2)) multiplies fp16 operands with f32 accumulation:
+ *     the activation operand is the exact Q8_K value d*q divided by a power of two,
+ *     the weight operand is the dequantised weight rounded to fp16 once.  There is no
+ *     int32 block sum on that path; results agree with the CPU path to about 3e-4 of
+ *     the output norm (1e-3 is the bound the tests hold it to), and a token's output
+ *     therefore depends, within that bound, on whether its batch took this path.
  */
 #ifndef ZMOE_B200_H
 #define ZMOE_B200_H
@@ -101,6 +110,20 @@ int zmoe_matmul_noalloc(int type, float *y, const float *x, const void *w, int S
 int zmoe_reserve(int rows, int I);
 /* status of the most recent kernel-launch-ABI call on this thread */
 int zmoe_last_status(void);
+/* The entry points of this section, the op hook of section 2 and zmoe_matmul_noalloc have no handle to
+ * report a device-side problem through: their kernels raise an error word in the library's per-device
+ * scratch when a bounded wait runs out (the output of that launch is then incomplete).  This call waits
+ * for the current device, reads those words and clears them: 0, or ZMOE_ERR_DEVICE_WAIT.
+ * Contract of the per-device scratch: host threads may call these entry points concurrently (the scratch
+ * is locked from sizing to enqueue, and is only reallocated after the device has drained), but all calls
+ * on one device share one set of buffers -- calls whose kernels may overlap on the GPU (different streams
+ * with no ordering between them) race on it, exactly as documented for zmoe_matmul_noalloc. */
+int zmoe_device_status(void);
+/* Self-test of that reporting path, for test suites: enqueues one warp that waits, with a limit of a few
+ * hundred polls, on a barrier nothing arrives on; the wait runs out, the warp raises the error word like a
+ * matmul kernel would and returns (no hang, no fault).  zmoe_device_status() must then report
+ * ZMOE_ERR_DEVICE_WAIT once. */
+int zmoe_selftest_wait_expiry(void *stream);
 
 /* =========================================================================
  * 2. ggml backend op hook -- replaces the hook the reference registers with
@@ -214,6 +237,13 @@ int zmoe_get_act(zmoe_ctx *ctx, int n_pairs, int d_ff, float *act_host);
 int zmoe_ctx_set_path(zmoe_ctx *ctx, int path);
 /* reads and clears the device error flag: 0, or ZMOE_ERR_DEVICE_WAIT */
 int zmoe_ctx_check(zmoe_ctx *ctx);
+/* Non-finite inputs seen by the fused SwiGLU epilogues of this context's expert FFN calls since the last
+ * clear: counts_host[0] = (gate, up) pairs with a NaN, counts_host[1] = pairs without NaN but with an
+ * infinity -- the counters of reference kernels/math/expert_activation.cu:42-44, which
+ * core/gpu_expert_executor.cpp:406-421 samples.  Synchronise the stream first; clear != 0 resets them. */
+int zmoe_ctx_bad_counts(zmoe_ctx *ctx, int32_t *counts_host, int clear);
+/* average pairs per expert from which zmoe_expert_ffn takes the tensor-core grouped GEMM when the path is 0 */
+int zmoe_gemm_min_pairs_per_expert(void);
 /* number of kernels this library has launched since load (all entry points) */
 uint64_t zmoe_kernel_launches(void);
 

@@ -22,7 +22,9 @@ def build(force=False):
     """Compile the oracle (and the reference shim when the reference checkout exists)."""
     if force or not os.path.exists(LIB_PATH):
         subprocess.check_call(["make", "-C", HERE, "-s", "libzmoe_oracle.so"])
-    ref_root = os.environ.get("ZMOE_REFERENCE_ROOT", "/root/reference")
+    # the reference checkout, where there is one: named by ZMOE_REFERENCE_ROOT, else looked for beside
+    # this repository (../reference); without it the `ref` target is skipped
+    ref_root = os.environ.get("ZMOE_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     if os.path.isdir(ref_root) and (force or not os.path.exists(REF_PATH)):
         subprocess.call(["make", "-C", HERE, "-s", "ref", "REF=" + ref_root])
 

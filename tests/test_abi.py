@@ -39,6 +39,8 @@ def test_argument_validation_needs_no_device():
     assert L.zmoe_quantize_q8_K(None, None, 1, 256, lib.Q4_K, None) == -1
     assert L.zmoe_block_isums(99, None, None, None, None, 1, 256, None) == -1
     assert L.zmoe_reserve(4, 100) == -1
+    assert L.zmoe_ctx_bad_counts(None, None, 0) == -1
+    assert L.zmoe_gemm_min_pairs_per_expert() == 24
     assert not L.zeromoe_install_f32_quant_graph_hook()
     assert not L.zmoe_f32_quant_hook(None, None, None, None, None, False)
 

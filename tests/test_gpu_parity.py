@@ -235,6 +235,7 @@ LAYER_CASES = [
     (2048, 768, 128, 8, (synth.Q4_K, synth.Q4_K, synth.Q4_K), 1),       # benchmark configuration 1, decode
     (2048, 768, 128, 8, (synth.Q4_K, synth.Q4_K, synth.Q4_K), 64),      # configuration 1, 64 tokens
     (4096, 1536, 128, 8, (synth.Q2_K, synth.Q2_K, synth.Q3_K), 1),      # configuration 2
+    (4096, 1536, 128, 8, (synth.Q2_K, synth.Q2_K, synth.Q3_K), 4),
     (4096, 1536, 128, 8, (synth.Q2_K, synth.Q2_K, synth.Q3_K), 16),
     (4096, 1536, 32, 8, (synth.IQ2_XXS, synth.IQ2_XXS, synth.IQ2_XXS), 5),   # configuration 3's types
     (1024, 512, 16, 4, (synth.Q2_K, synth.Q4_K, synth.Q3_K), 7),        # gate and up of different types

@@ -4,8 +4,10 @@
 #include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <new>
+#include <utility>
 
 #include "zmoe_common.cuh"
 #include "zmoe_internal.h"
@@ -27,12 +29,10 @@ int dev_alloc(T **p, size_t n) {
     return ok(cudaMalloc(reinterpret_cast<void **>(p), n * sizeof(T)));
 }
 
-int sm_count() {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    return n;
-}
+int sm_count() { return zmoe::device_sm_count(); }
+
+// pairs per expert, averaged over the call, from which the layer entry takes the tensor-core grouped GEMM
+constexpr int kGemmMinPairsPerExpert = 24;
 
 struct PlanStore {
     PlanBuffers b;
@@ -63,6 +63,39 @@ struct PlanStore {
 
 }  // namespace
 
+namespace zmoe {
+
+int device_sm_count() {
+    constexpr int kMax = 64;
+    static std::atomic<int> cache[kMax];
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < kMax && (n = cache[dev].load(std::memory_order_relaxed)) > 0) return n;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < kMax) cache[dev].store(n, std::memory_order_relaxed);
+    return n;
+}
+
+void count_launches(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+void set_last_status(int rc) { tl_status = rc; }
+
+int raise_dynamic_smem(const void *fn, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, size_t> done;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return ZMOE_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &have = done[std::make_pair(fn, dev)];
+    if (have < bytes) {
+        if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
+            return ZMOE_ERR_CUDA;
+        have = bytes;
+    }
+    return ZMOE_OK;
+}
+
+}  // namespace zmoe
+
 // ---------------------------------------------------------------------------
 // context and layer
 // ---------------------------------------------------------------------------
@@ -88,6 +121,7 @@ struct zmoe_ctx {
     float *weights = nullptr;  // [T, K]
     PlanStore plan;
     int *err = nullptr;
+    int *bad = nullptr;        // [2] NaN / Inf inputs seen by the fused SwiGLU epilogues
     unsigned *ticket = nullptr;
     float *x_stage = nullptr, *out_stage = nullptr;  // device staging of the host entry
     cudaStream_t host_stream = nullptr;
@@ -135,6 +169,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     rc |= dev_alloc(&c->weights, P);
     rc |= c->plan.alloc(max_experts, (int)P);
     rc |= dev_alloc(&c->err, 1);
+    rc |= dev_alloc(&c->bad, 2);
     rc |= dev_alloc(&c->ticket, 1 + ROUTER_MAX_GROUPS);
     rc |= dev_alloc(&c->x_stage, (size_t)max_tokens * max_d_model);
     rc |= dev_alloc(&c->out_stage, (size_t)max_tokens * max_d_model);
@@ -142,6 +177,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     rc |= ok(cudaHostAlloc(reinterpret_cast<void **>(&c->err_host), sizeof(int), cudaHostAllocDefault));
     if (!rc) {
         rc |= ok(cudaMemset(c->err, 0, sizeof(int)));
+        rc |= ok(cudaMemset(c->bad, 0, 2 * sizeof(int)));
         rc |= ok(cudaMemset(c->ticket, 0, (1 + ROUTER_MAX_GROUPS) * sizeof(unsigned)));
         rc |= ok(cudaMemset(c->plan.b.hdr, 0, 4 * sizeof(int)));
         rc |= ok(cudaMemset(c->zero_ids, 0, (size_t)max_tokens * sizeof(int32_t)));
@@ -169,7 +205,7 @@ void zmoe_ctx_destroy(zmoe_ctx *c) {
     cudaFree(c->zero_ids); cudaFree(c->one_w);
     cudaFree(c->xq_f16); cudaFree(c->actq_f16); cudaFree(c->xscale); cudaFree(c->actscale);
     cudaFree(c->q8x); cudaFree(c->q8x2); cudaFree(c->act); cudaFree(c->act2); cudaFree(c->q8act); cudaFree(c->ydown);
-    cudaFree(c->logits); cudaFree(c->ids); cudaFree(c->weights); cudaFree(c->err); cudaFree(c->ticket);
+    cudaFree(c->logits); cudaFree(c->ids); cudaFree(c->weights); cudaFree(c->err); cudaFree(c->bad); cudaFree(c->ticket);
     cudaFree(c->x_stage); cudaFree(c->out_stage);
     c->plan.release();
     if (c->host_stream) cudaStreamDestroy(c->host_stream);
@@ -309,6 +345,7 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
     MmidLaunch m;
     m.plan = c->plan.b;
     m.err = c->err;
+    m.bad = c->bad;
     m.n_sm = c->n_sm;
     m.clamp = d.swiglu_clamp;
     m.clamp_fused = d.swiglu_clamp_fused;
@@ -317,11 +354,11 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
     // many pairs per expert: the contraction is compute-bound and goes to the tensor cores
     const bool gemm_ok = L->dual && c->x_last && gemm_sm100_supported(d.gate.type, d.d_model, d.d_ff) &&
                          gemm_sm100_supported(d.down.type, d.d_ff, d.d_model) && d.n_experts <= 512;
-    const bool use_gemm = gemm_ok && (c->path == 2 || (c->path == 0 && (long)P >= 24L * d.n_experts));
+    const bool use_gemm = gemm_ok && (c->path == 2 || (c->path == 0 && (long)P >= (long)kGemmMinPairsPerExpert * d.n_experts));
     if (use_gemm) {
         if (ev_before) cudaEventRecord(static_cast<cudaEvent_t>(ev_before), st);
         GemmLaunch g;
-        g.plan = c->plan.b; g.err = c->err; g.n_sm = c->n_sm;
+        g.plan = c->plan.b; g.err = c->err; g.bad = c->bad; g.n_sm = c->n_sm;
         g.clamp = d.swiglu_clamp; g.clamp_fused = d.swiglu_clamp_fused;
         rc = launch_q8_roundtrip_f16(c->x_last, d.d_model, c->xq_f16, c->xscale, c->plan.b, P, d.topk, d.d_model, st);
         g.type = d.gate.type; g.dual = true;
@@ -369,7 +406,7 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         m.type = d.gate.type; m.w0 = d.gate.data_dev; m.stride0 = d.gate.expert_stride; m.total0 = L->bytes_gate; m.y = gbuf;
         if (!rc) rc = launch_mmid(m, L->g_gu, st);
         if (!rc) {
-            launch_expert_swiglu(c->act, gbuf, ubuf, P * d.d_ff, d.swiglu_clamp, d.swiglu_clamp_fused, nullptr, stream);
+            launch_expert_swiglu(c->act, gbuf, ubuf, P * d.d_ff, d.swiglu_clamp, d.swiglu_clamp_fused, c->bad, stream);
             rc = ok(cudaPeekAtLastError());
         }
         g_launches += 3;
@@ -475,6 +512,16 @@ int zmoe_ctx_check(zmoe_ctx *c) {
     return ZMOE_OK;
 }
 
+int zmoe_ctx_bad_counts(zmoe_ctx *c, int32_t *counts_host, int clear) {
+    if (!c || !counts_host) return ZMOE_ERR_ARG;
+    if (cudaMemcpy(counts_host, c->bad, 2 * sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return ZMOE_ERR_CUDA;
+    if (clear && (counts_host[0] | counts_host[1]) && cudaMemset(c->bad, 0, 2 * sizeof(int)) != cudaSuccess)
+        return ZMOE_ERR_CUDA;
+    return ZMOE_OK;
+}
+
+int zmoe_gemm_min_pairs_per_expert(void) { return kGemmMinPairsPerExpert; }
+
 uint64_t zmoe_kernel_launches(void) { return g_launches.load(); }
 
 }  // extern "C"
@@ -497,12 +544,16 @@ constexpr int kMaxDevices = 64;
 DeviceScratch g_scratch[kMaxDevices];
 std::mutex g_scratch_mu;
 
-// makes sure the current device's scratch can hold `rows` packed rows of I
-// elements, a plan for E experts and P pairs
-int scratch_get(int rows, int I, int E, int P, DeviceScratch **out) {
+using ScratchLock = std::unique_lock<std::mutex>;
+
+// Makes sure the current device's scratch can hold `rows` packed rows of I elements, a plan for E experts
+// and P pairs, and hands it out LOCKED: the caller keeps `lock` until its kernels are enqueued, so no other
+// host thread can grow (free and reallocate) the buffers between this call's launches.  Growing waits for
+// the device first, so kernels already enqueued never see a freed buffer.
+int scratch_get(int rows, int I, int E, int P, DeviceScratch **out, ScratchLock &lock) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return ZMOE_ERR_CUDA;
-    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    lock = ScratchLock(g_scratch_mu);
     DeviceScratch &s = g_scratch[dev];
     if (!s.n_sm) s.n_sm = sm_count();
     const size_t need = (size_t)rows * q8row_stride(I);
@@ -536,7 +587,8 @@ int dense_matmul(int type, float *y, const float *x, int ldx, const void *w, int
     int rc = mmid_geometry(type, I, O, false, &g);
     if (rc) return rc;
     DeviceScratch *s;
-    rc = scratch_get(S, I, 1, S, &s);
+    ScratchLock lock;
+    rc = scratch_get(S, I, 1, S, &s, lock);
     if (rc) return rc;
     const int nrt = (O + g.R - 1) / g.R;
     rc = launch_quantize_rows(x, ldx, s->q8, S, I, q8_layout_of(type), st);
@@ -571,6 +623,19 @@ void fill_bad_rows(float *y, int ldy, const int32_t *ids, int P, int E, int O, c
     fill_bad_rows_kernel<<<P, 128, 0, st>>>(y, ldy, ids, P, E, O);
 }
 
+// One warp waits, with a short limit, on a barrier that nobody arrives on: the wait runs out, the warp raises
+// the error word exactly as the matmul kernels do, and returns.  Exists so that the path from an expired
+// device-side wait to ZMOE_ERR_DEVICE_WAIT can be exercised without a hang or a fault.
+__global__ void wait_expiry_probe_kernel(int *err) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    if (!mbar_wait(&bar, 0, 256) && threadIdx.x == 0) atomicExch(err, 1);
+}
+
 __global__ void gather_ids_kernel(const uint8_t *src, size_t nb0, size_t nb1, int32_t *dst, int K, int T) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= K * T) return;
@@ -585,10 +650,43 @@ extern "C" {
 int zmoe_reserve(int rows, int I) {
     if (rows <= 0 || I <= 0 || I % QK_K) return ZMOE_ERR_ARG;
     DeviceScratch *s;
-    return scratch_get(rows, I, 1, rows, &s);
+    ScratchLock lock;
+    return scratch_get(rows, I, 1, rows, &s, lock);
 }
 
 int zmoe_last_status(void) { return tl_status; }
+
+int zmoe_device_status(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return ZMOE_ERR_CUDA;
+    if (cudaDeviceSynchronize() != cudaSuccess) return ZMOE_ERR_CUDA;
+    int seen = 0;
+    {
+        ScratchLock lock(g_scratch_mu);
+        DeviceScratch &s = g_scratch[dev];
+        if (s.err) {
+            int e = 0;
+            if (cudaMemcpy(&e, s.err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return ZMOE_ERR_CUDA;
+            if (e) {
+                seen = e;
+                if (cudaMemset(s.err, 0, sizeof(int)) != cudaSuccess) return ZMOE_ERR_CUDA;
+            }
+        }
+    }
+    int e2 = 0;
+    if (noalloc_take_error(&e2)) return ZMOE_ERR_CUDA;
+    return (seen || e2) ? ZMOE_ERR_DEVICE_WAIT : ZMOE_OK;
+}
+
+int zmoe_selftest_wait_expiry(void *stream) {
+    DeviceScratch *s;
+    ScratchLock lock;
+    int rc = scratch_get(1, QK_K, 1, 1, &s, lock);
+    if (rc) return rc;
+    wait_expiry_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(s->err);
+    g_launches += 1;
+    return ok(cudaPeekAtLastError());
+}
 
 #define ZMOE_DENSE(name, type)                                                                         \
     void name##_stream(float *y, const float *x, const void *w, int S, int I, int O, void *stream) {     \
@@ -631,8 +729,9 @@ bool zmoe_f32_quant_hook(const zmoe_tensor *w, const zmoe_tensor *x, const zmoe_
         if ((reinterpret_cast<size_t>(w->data) & 15) || (w->nb[2] & 15)) return false;
         if (!execute) return true;
         DeviceScratch *s;
+        ScratchLock lock;
         const int rows = T * xr;
-        if (scratch_get(rows, I, E, K * T, &s)) return false;
+        if (scratch_get(rows, I, E, K * T, &s, lock)) return false;
         const int ldx = xr == 1 ? (int)(x->nb[2] / 4) : (int)(x->nb[1] / 4);
         int rc = launch_quantize_rows(static_cast<const float *>(x->data), ldx, s->q8, rows, I, q8_layout_of(w->type), st);
         gather_ids_kernel<<<(K * T + 255) / 256, 256, 0, st>>>(static_cast<const uint8_t *>(ids->data), ids->nb[0],
@@ -681,7 +780,8 @@ int zmoe_quantize_q8_K(const float *x_dev, void *blocks_dev, int rows, int I, in
     if (!x_dev || !blocks_dev || rows <= 0 || I <= 0 || I % QK_K) return ZMOE_ERR_ARG;
     if (block_bytes(for_type) == 0) return ZMOE_ERR_TYPE;
     DeviceScratch *s;
-    int rc = scratch_get(rows, I, 1, rows, &s);
+    ScratchLock lock;
+    int rc = scratch_get(rows, I, 1, rows, &s, lock);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // quantise into the packed row layout that weight format uses, then regroup into ggml blocks
     const int layout = q8_layout_of(for_type);
@@ -696,7 +796,8 @@ int zmoe_block_isums(int type, const void *w_dev, const float *x_dev, int32_t *i
     if (!w_dev || !x_dev || !isum_dev || !msum_dev || rows <= 0 || I <= 0 || I % QK_K) return ZMOE_ERR_ARG;
     if (block_bytes(type) == 0) return ZMOE_ERR_TYPE;
     DeviceScratch *s;
-    int rc = scratch_get(rows, I, 1, rows, &s);
+    ScratchLock lock;
+    int rc = scratch_get(rows, I, 1, rows, &s, lock);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!rc) rc = launch_quantize_rows(x_dev, I, s->q8, rows, I, q8_layout_of(type), st);
     if (!rc) rc = launch_block_isums(type, w_dev, s->q8, isum_dev, msum_dev, rows, I, st);

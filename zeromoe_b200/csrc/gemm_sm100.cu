@@ -92,7 +92,8 @@ int launch_q8_roundtrip_f16(const float *x, int ldx, void *out_f16, float *scale
                             int max_rows, int xdiv, int I, cudaStream_t st) {
     if (max_rows <= 0) return ZMOE_OK;
     if (I / QK_K > 8 * RT_MAXB) return ZMOE_ERR_SHAPE;
-    const int grid = max_rows < 148 * 8 ? max_rows : 148 * 8;
+    const int cap = 8 * device_sm_count();
+    const int grid = max_rows < cap ? max_rows : cap;
     return launch_pdl(q8_roundtrip_f16_kernel, dim3((unsigned)grid), dim3(256), 0, st, x, ldx,
                       static_cast<__half *>(out_f16), scale, (const int *)plan.hdr, (const int *)plan.slot, xdiv,
                       I) == cudaSuccess
@@ -193,6 +194,7 @@ int launch_gemm_sm100(const GemmLaunch &L, cudaStream_t st) {
     p.clamp = L.clamp; p.clamp_fused = L.clamp_fused;
     p.nstage = nstage;
     p.err = L.err;
+    p.bad = L.dual ? L.bad : nullptr;
     return launch_pdl(fn, dim3(L.n_sm), dim3(GEMM_THREADS), smem, st, p, maps) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
 }
 

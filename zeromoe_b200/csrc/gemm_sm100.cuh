@@ -50,6 +50,7 @@ struct GemmParams {
     int clamp_fused;
     int nstage;
     int *err;
+    int *bad;                    // DUAL: [2] counters of NaN / Inf gate or up values, or null
 };
 
 // Activation tile maps with boxes of 32, 64, 128 and 256 rows: a tile loads the smallest box that covers
@@ -259,7 +260,11 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
                     const float sc = __shfl_sync(0xffffffffu, my_sc, j);
                     if (c0 + j < np) {
                         float v = __uint_as_float(g[j]) * sc;
-                        if (DUAL) v = swiglu_f(v, __uint_as_float(u[j]) * sc, p.clamp, p.clamp_fused);
+                        if (DUAL) {
+                            const float uv = __uint_as_float(u[j]) * sc;
+                            count_bad(p.bad, v, uv);
+                            v = swiglu_f(v, uv, p.clamp, p.clamp_fused);
+                        }
                         p.y[(size_t)pair * p.ldy + f] = v;
                     }
                 }

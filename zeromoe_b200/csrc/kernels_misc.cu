@@ -119,11 +119,8 @@ int launch_router_decode(const RouterArgs &a, cudaStream_t st) {
     const size_t smem = (size_t)2 * (ROUTER_THREADS / 32) * a.E * sizeof(float) + (size_t)2 * (a.E + 1) * sizeof(int) +
                         (a.T * a.K <= ROUTER_IDS_SMEM ? (size_t)a.T * a.K * sizeof(int) : 0);
     if (smem > 200 * 1024) return ZMOE_ERR_SHAPE;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(router_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr_done = true;
-    }
+    if (raise_dynamic_smem(reinterpret_cast<const void *>(router_decode_kernel), 200 * 1024) != ZMOE_OK)
+        return ZMOE_ERR_CUDA;
     const long grid = (long)a.E * ((a.T + ROUTER_TPB - 1) / ROUTER_TPB);
     if (grid > 0x7fffffffL) return ZMOE_ERR_SHAPE;
     return launch_pdl(router_decode_kernel, dim3((unsigned)grid), dim3(ROUTER_THREADS), smem, st, a) == cudaSuccess
@@ -298,7 +295,8 @@ int launch_quantize_rows(const float *x, int ldx, uint8_t *q8, int rows, int I, 
     if (rows <= 0) return ZMOE_OK;
     const long blocks = (long)rows * (I / QK_K);
     long grid = (blocks + 7) / 8;
-    if (grid > 148 * 8) grid = 148 * 8;
+    const long cap = 8L * device_sm_count();
+    if (grid > cap) grid = cap;
     return launch_pdl(quantize_rows_kernel, dim3((unsigned)grid), dim3(256), 0, st, x, ldx, q8, rows, I, layout) == cudaSuccess
                ? ZMOE_OK
                : ZMOE_ERR_CUDA;
@@ -379,8 +377,9 @@ int launch_combine(float *out, const float *y, const float *w, const int32_t *id
     // one float4 per thread where that still fills the machine: a short batch is bound by the trip to L2
     long grid = (n + 255) / 256;
     int threads = 256;
-    if (grid < 148) { threads = 64; grid = (n + 63) / 64; }
-    if (grid > 148 * 8) grid = 148 * 8;
+    const int n_sm = device_sm_count();
+    if (grid < n_sm) { threads = 64; grid = (n + 63) / 64; }
+    if (grid > 8L * n_sm) grid = 8L * n_sm;
     auto fn = K <= 8 ? combine_kernel<8> : K <= 16 ? combine_kernel<16> : combine_kernel<0>;
     return launch_pdl(fn, dim3((unsigned)grid), dim3(threads), 0, st, out, y, w, ids, T, K, D, E, accumulate) == cudaSuccess
                ? ZMOE_OK
@@ -451,32 +450,84 @@ int launch_block_isums(int type, const void *w, const uint8_t *q8, int32_t *isum
 // ------------------------------------------------------------------------
 namespace {
 
-// reference kernels/math/expert_activation.cu:31-59
-__global__ void expert_swiglu_kernel(float *__restrict__ prod, const float *__restrict__ gate,
-                                     const float *__restrict__ up, int n, float clamp, int fused,
-                                     int *__restrict__ bad) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const float g0 = gate[i], u0 = up[i];
-    if (bad) {
-        if (isnan(g0) || isnan(u0)) atomicAdd(&bad[0], 1);
-        else if (isinf(g0) || isinf(u0)) atomicAdd(&bad[1], 1);
+// prod = SwiGLU(gate, up) over n elements, four per thread per step, grid-stride.  Same values as
+// reference kernels/math/expert_activation.cu:46-58 (expf, the two clamp forms).  Non-finite inputs are
+// counted like the reference does (bad[0]: an input is NaN, bad[1]: none is NaN and one is infinite),
+// but a warp adds its counts with one atomic per counter instead of one per element.
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(float *__restrict__ prod, const float *__restrict__ gate,
+                                                          const float *__restrict__ up, int n, float clamp, int fused,
+                                                          int *__restrict__ bad, int vec_ok) {
+    const int lane = threadIdx.x & 31;
+    int n_nan = 0, n_inf = 0;
+    auto one = [&](float g, float u) -> float {
+        if (bad) {
+            const bool isn = (g != g) || (u != u);
+            n_nan += isn;
+            n_inf += !isn && (isinf(g) || isinf(u));
+        }
+        return zmoe::swiglu_f(g, u, clamp, fused);
+    };
+    const long stride = (long)gridDim.x * blockDim.x;
+    const long first = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int n4 = vec_ok ? n / 4 : 0;
+    for (long i = first; i < n4; i += stride) {
+        const float4 g = reinterpret_cast<const float4 *>(gate)[i], u = reinterpret_cast<const float4 *>(up)[i];
+        float4 o;
+        o.x = one(g.x, u.x); o.y = one(g.y, u.y); o.z = one(g.z, u.z); o.w = one(g.w, u.w);
+        reinterpret_cast<float4 *>(prod)[i] = o;
     }
-    prod[i] = zmoe::swiglu_f(g0, u0, clamp, fused);
+    for (long i = 4L * n4 + first; i < n; i += stride) prod[i] = one(gate[i], up[i]);
+    if (bad) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            n_nan += __shfl_xor_sync(0xffffffffu, n_nan, off);
+            n_inf += __shfl_xor_sync(0xffffffffu, n_inf, off);
+        }
+        if (lane == 0) {
+            if (n_nan) atomicAdd(&bad[0], n_nan);
+            if (n_inf) atomicAdd(&bad[1], n_inf);
+        }
+    }
 }
 
-// reference kernels/math/expert_accum.cu:22-37: dst[tok[i],:] += w[i]*src[i,:]; rows of
-// one call target distinct tokens, calls are ordered by the stream
-__global__ void expert_scatter_accum_kernel(const float *__restrict__ src, const int *__restrict__ tok,
-                                            const float *__restrict__ w, float *__restrict__ dst, int n, int D, int S) {
-    const int i = blockIdx.x;
-    if (i >= n) return;
-    const int s = tok[i];
+// dst[tok[i], :] += w[i] * src[i, :] for the n rows of one call (w == nullptr: plain add).  Contract of
+// reference kernels/math/expert_accum.cu:22-37: rows of one call name distinct tokens, calls are ordered
+// by the stream, a token outside [0, S) is skipped, no atomics.  A warp walks a row four floats per lane;
+// the grid covers rows x row chunks so that a short call still fills the machine.
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const float *__restrict__ src, const int *__restrict__ tok,
+                                                           const float *__restrict__ w, float *__restrict__ dst, int n,
+                                                           int D, int S, int chunks, int vec_ok) {
+    const int row = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
+    if (row >= n) return;
+    const int s = tok[row];
     if (s < 0 || s >= S) return;
-    const float wt = w ? w[i] : 1.0f;
-    const float *sr = src + (size_t)i * D;
+    const float wt = w ? w[row] : 1.0f;
+    const float *sr = src + (size_t)row * D;
     float *ds = dst + (size_t)s * D;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) ds[d] += wt * sr[d];
+    const int per = (D + chunks - 1) / chunks;
+    const int d0 = chunk * per, d1 = min(D, d0 + per);
+    if (vec_ok && (per & 3) == 0) {
+        for (int d = d0 + 4 * threadIdx.x; d + 3 < d1; d += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4 *>(sr + d);
+            float4 o = *reinterpret_cast<float4 *>(ds + d);
+            o.x = fmaf(wt, v.x, o.x); o.y = fmaf(wt, v.y, o.y); o.z = fmaf(wt, v.z, o.z); o.w = fmaf(wt, v.w, o.w);
+            *reinterpret_cast<float4 *>(ds + d) = o;
+        }
+        const int tail = d0 + ((d1 - d0) & ~3);
+        for (int d = tail + threadIdx.x; d < d1; d += blockDim.x) ds[d] = fmaf(wt, sr[d], ds[d]);
+    } else {
+        for (int d = d0 + threadIdx.x; d < d1; d += blockDim.x) ds[d] = fmaf(wt, sr[d], ds[d]);
+    }
+}
+
+void scatter_rows(const float *src, const int *tok, const float *w, float *dst, int n, int D, int S, cudaStream_t st) {
+    if (n <= 0 || D <= 0) return;
+    const int n_sm = zmoe::device_sm_count();
+    int chunks = 1;
+    while (n * chunks < 2 * n_sm && D / (chunks * 2) >= 256) chunks *= 2;
+    const int vec_ok = (D % 4 == 0) && ((reinterpret_cast<size_t>(src) | reinterpret_cast<size_t>(dst)) % 16 == 0);
+    const int threads = D / chunks >= 1024 ? 256 : 64;
+    scatter_rows_kernel<<<n * chunks, threads, 0, st>>>(src, tok, w, dst, n, D, S, chunks, vec_ok);
 }
 
 // reference kernels/models/glm5next_router.cu:33-93, one warp per token
@@ -498,28 +549,49 @@ extern "C" {
 void launch_expert_swiglu(float *prod, const float *gate, const float *up, int n, float clamp, int fused, int *d_bad,
                           void *stream) {
     if (n <= 0) return;
-    expert_swiglu_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(prod, gate, up, n, clamp, fused, d_bad);
+    const int n_sm = zmoe::device_sm_count();
+    long grid = ((long)n / 4 + 255) / 256;
+    if (grid < 1) grid = 1;
+    if (grid > 8L * n_sm) grid = 8L * n_sm;
+    const int vec_ok =
+        ((reinterpret_cast<size_t>(prod) | reinterpret_cast<size_t>(gate) | reinterpret_cast<size_t>(up)) % 16) == 0;
+    swiglu_rows_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(prod, gate, up, n, clamp, fused,
+                                                                                     d_bad, vec_ok);
+    zmoe::count_launches(1);
 }
 
 void launch_expert_scatter_accum(const float *src, const int *tok, const float *w, float *dst, int n, int D, int S,
                                  void *stream) {
-    if (n <= 0 || D <= 0) return;
-    expert_scatter_accum_kernel<<<n, D < 256 ? 64 : 256, 0, static_cast<cudaStream_t>(stream)>>>(src, tok, w, dst, n, D, S);
+    scatter_rows(src, tok, w, dst, n, D, S, static_cast<cudaStream_t>(stream));
+    zmoe::count_launches(1);
 }
 
 void launch_expert_scatter_add(const float *src, const int *tok, float *dst, int n, int D, int S,
                                void *stream) {
-    if (n <= 0 || D <= 0) return;
-    expert_scatter_accum_kernel<<<n, D < 256 ? 64 : 256, 0, static_cast<cudaStream_t>(stream)>>>(src, tok, nullptr, dst, n, D, S);
+    scatter_rows(src, tok, nullptr, dst, n, D, S, static_cast<cudaStream_t>(stream));
+    zmoe::count_launches(1);
 }
 
 void launch_glm5next_router_topk(float *logits, const float *bias, int32_t *ids, float *weights, int S, int n_experts,
                                  int topk, int gating_func, int normalize, float weight_scale, void *stream) {
-    if (S <= 0 || n_experts <= 0 || topk <= 0 || topk > n_experts) return;
+    if (!logits || !ids || !weights || S <= 0 || n_experts <= 0 || topk <= 0 || topk > n_experts) {
+        zmoe::set_last_status(ZMOE_ERR_ARG);
+        return;
+    }
     zmoe::RouterSpec sp{n_experts, topk, gating_func, normalize, weight_scale, 0, 0};
     const size_t smem = (size_t)8 * n_experts * sizeof(float);
-    if (smem > 48 * 1024) return;
+    if (smem > 200 * 1024) {
+        zmoe::set_last_status(ZMOE_ERR_SHAPE);
+        return;
+    }
+    if (smem > 48 * 1024 &&
+        zmoe::raise_dynamic_smem(reinterpret_cast<const void *>(router_topk_kernel), smem) != ZMOE_OK) {
+        zmoe::set_last_status(ZMOE_ERR_CUDA);
+        return;
+    }
     router_topk_kernel<<<(S + 3) / 4, 128, smem, static_cast<cudaStream_t>(stream)>>>(logits, bias, ids, weights, S, sp);
+    zmoe::count_launches(1);
+    zmoe::set_last_status(cudaPeekAtLastError() == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA);
 }
 
 }  // extern "C"

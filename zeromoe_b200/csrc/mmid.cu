@@ -161,6 +161,7 @@ int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
     p.mma_hpw = mma_hpw;
     p.mma_rdiv = (65536 + g.R - 1) / g.R;
     p.err = L.err;
+    p.bad = L.dual ? L.bad : nullptr;
     return launch_pdl(fn, dim3(L.n_sm), dim3(32 * (g.ncw + 1)), g.smem_bytes, st, p) == cudaSuccess ? ZMOE_OK
                                                                                                    : ZMOE_ERR_CUDA;
 }

@@ -25,6 +25,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <math_constants.h>
 
 #include "mmid_mma.cuh"
 #include "quant_units.cuh"
@@ -73,6 +74,7 @@ struct MmidParams {
     int mma_hpw;                // multi-token path: half super-blocks per warp
     int mma_rdiv;               // multi-token path: ceil(65536 / R), for dividing a thread index by R
     int *err;                   // device error flag
+    int *bad;                   // DUAL: [2] counters of NaN / Inf gate or up values, or null
     int use_tmap;               // tiles come through tm0 / tm1 (rows padded to rbs = rb + 16 by the copy)
     alignas(64) CUtensorMap tm0, tm1;
 };
@@ -109,6 +111,16 @@ __device__ __forceinline__ float swiglu_f(float g, float u, float clamp, int fus
         if (clamp > 0.0f) out = fmaxf(-clamp, fminf(clamp, out));
     }
     return out;
+}
+
+// Non-finite inputs of the fused SwiGLU, counted as reference kernels/math/expert_activation.cu:42-44
+// does (bad[0]: one of the two is NaN; bad[1]: none is NaN, one is infinite).  The test is one
+// instruction on the common path; the atomics run only when something is wrong.
+__device__ __forceinline__ void count_bad(int *bad, float g, float u) {
+    if (bad && !(fabsf(g) < CUDART_INF_F && fabsf(u) < CUDART_INF_F)) {
+        if (g != g || u != u) atomicAdd(&bad[0], 1);
+        else atomicAdd(&bad[1], 1);
+    }
 }
 
 // issue the copy of one weight tile; returns bytes that will complete on `bar`
@@ -297,7 +309,10 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const __grid_co
             if (sl < parked) {
                 float a0 = park0, a1 = park1;
                 if (TYPE == IQ2_XXS) { a0 *= 0.125f; a1 *= 0.125f; }
-                if (park_idx != (size_t)-1) p.y[park_idx] = DUAL ? swiglu_f(a0, a1, p.clamp, p.clamp_fused) : a0;
+                if (park_idx != (size_t)-1) {
+                    if (DUAL) count_bad(p.bad, a0, a1);
+                    p.y[park_idx] = DUAL ? swiglu_f(a0, a1, p.clamp, p.clamp_fused) : a0;
+                }
             }
             parked = 0;
         };
@@ -328,6 +343,7 @@ __global__ void __launch_bounds__(32 * (NCW + 1), 1) mmid_kernel(const __grid_co
                     a0 += pr[i * PART];
                     if (DUAL) a1 += pr[(ks_n + i) * PART];
                 }
+                if (DUAL) count_bad(p.bad, a0, a1);
                 p.y[pend_idx] = DUAL ? swiglu_f(a0, a1, p.clamp, p.clamp_fused) : a0;
             }
             return true;

@@ -71,8 +71,9 @@ extern "C" int zmoe_matmul_noalloc(int type, float *y, const float *x, const voi
         cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
         return ZMOE_ERR_CUDA;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // the array keeps whatever the last call left: the error flag and the plan header must start at zero
-    if (cudaMemsetAsync(base, 0, kOffSlot, st) != cudaSuccess) return ZMOE_ERR_CUDA;
+    // the array keeps whatever the last call left: the plan header must start at zero.  The error word in
+    // front of it is left alone: it stays set until zmoe_device_status() has reported and cleared it.
+    if (cudaMemsetAsync(base + kOffHdr, 0, kOffSlot - kOffHdr, st) != cudaSuccess) return ZMOE_ERR_CUDA;
     PlanBuffers plan;
     plan.hdr = reinterpret_cast<int *>(base + kOffHdr);
     plan.active = reinterpret_cast<int *>(base + kOffActive);
@@ -103,5 +104,22 @@ extern "C" int zmoe_matmul_noalloc(int type, float *y, const float *x, const voi
     m.err = reinterpret_cast<int *>(base + kOffErr);
     m.n_sm = n_sm;
     m.multi = S > 1;
+    count_launches(3);
     return launch_mmid(m, g, st);
+}
+
+// the error word of this device's array, read and cleared (the caller has synchronised the device)
+int zmoe::noalloc_take_error(int *out) {
+    *out = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return ZMOE_ERR_CUDA;
+    unsigned char *base;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        base = g_base[dev];
+    }
+    if (!base) return ZMOE_OK;   // the entry point has not run here: nothing to report
+    if (cudaMemcpy(out, base + kOffErr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return ZMOE_ERR_CUDA;
+    if (*out && cudaMemset(base + kOffErr, 0, sizeof(int)) != cudaSuccess) return ZMOE_ERR_CUDA;
+    return ZMOE_OK;
 }

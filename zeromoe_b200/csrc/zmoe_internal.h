@@ -11,6 +11,19 @@
 
 namespace zmoe {
 
+// ---- small host services shared by the .cu files (implemented in api.cu) ----
+// multiprocessor count of the current device (cached per device); 0 on failure
+int device_sm_count();
+// adds to the counter behind zmoe_kernel_launches()
+void count_launches(uint64_t n);
+// what zmoe_last_status() returns on this thread
+void set_last_status(int rc);
+// raises a kernel's dynamic shared-memory limit to at least `bytes` on the current device (the attribute
+// is per function and per device; remembered under a mutex)
+int raise_dynamic_smem(const void *fn, size_t bytes);
+// error word of the no-allocation entry point on the current device, read and cleared; 0 when that entry
+// point has not run on this device (implemented in noalloc.cu)
+int noalloc_take_error(int *out);
 
 // device-resident routing plan buffers
 struct PlanBuffers {
@@ -65,6 +78,7 @@ struct MmidLaunch {
     float clamp;
     int clamp_fused;
     int *err;
+    int *bad = nullptr;    // [2] NaN / Inf counters of the fused SwiGLU epilogue, or null
     int n_sm;
     bool multi = false;    // some expert may hold two or more pairs: allow the tensor-core consumer path
     // optional tiled maps of w0 / w1 (make_rows_map) that deliver tiles with padded rows in one copy
@@ -91,6 +105,7 @@ struct GemmLaunch {
     float clamp;
     int clamp_fused;
     int *err;
+    int *bad = nullptr;    // [2] NaN / Inf counters of the fused SwiGLU epilogue, or null
     int n_sm;
 };
 bool gemm_sm100_supported(int type, int I, int O);

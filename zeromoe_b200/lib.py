@@ -25,6 +25,7 @@ EXPORTS = [
     "zmoe_set_routes", "zmoe_set_routes_window", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_dense_ffn", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
     "zmoe_get_expert_freq", "zmoe_copy_routes", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_set_path", "zmoe_ctx_check", "zmoe_kernel_launches",
     "zmoe_quantize_q8_K", "zmoe_block_isums",
+    "zmoe_device_status", "zmoe_selftest_wait_expiry", "zmoe_ctx_bad_counts", "zmoe_gemm_min_pairs_per_expert",
 ]
 
 
@@ -109,6 +110,8 @@ def load():
     L.zmoe_ctx_set_path.argtypes = [vp, i]
     L.zmoe_quantize_q8_K.argtypes = [vp, vp, i, i, i, vp]
     L.zmoe_block_isums.argtypes = [i, vp, vp, vp, vp, i, i, vp]
+    L.zmoe_selftest_wait_expiry.argtypes = [vp]
+    L.zmoe_ctx_bad_counts.argtypes = [vp, vp, i]
     _lib = L
     return L
 
@@ -160,6 +163,13 @@ class Context:
         f = np.zeros(E, dtype=np.int32)
         check(load().zmoe_get_expert_freq(self.h, E, f.ctypes.data_as(C.c_void_p)), "zmoe_get_expert_freq")
         return f
+
+    def bad_counts(self, clear=True):
+        """(pairs with a NaN, pairs with an infinity) seen by the fused SwiGLU epilogues"""
+        c = np.zeros(2, dtype=np.int32)
+        check(load().zmoe_ctx_bad_counts(self.h, c.ctypes.data_as(C.c_void_p), 1 if clear else 0),
+              "zmoe_ctx_bad_counts")
+        return int(c[0]), int(c[1])
 
     def probs(self, T, E):
         p = np.zeros((T, E), dtype=np.float32)
