@@ -360,6 +360,7 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         GemmLaunch g;
         g.plan = c->plan.b; g.err = c->err; g.bad = c->bad; g.n_sm = c->n_sm;
         g.clamp = d.swiglu_clamp; g.clamp_fused = d.swiglu_clamp_fused;
+        g.n_experts = d.n_experts;
         rc = launch_q8_roundtrip_f16(c->x_last, d.d_model, c->xq_f16, c->xscale, c->plan.b, P, d.topk, d.d_model, st);
         g.type = d.gate.type; g.dual = true;
         g.w0 = d.gate.data_dev; g.w1 = d.up.data_dev;

@@ -1,9 +1,9 @@
 // dequant_f16.cuh -- 32 consecutive weights of a quantised row -> 32 fp16 values (four
 // 16-byte chunks).  Used by the prefill grouped GEMM to build its A tiles in shared memory.
 //
-// Split in two so that the global loads of the next k-step can be in flight while the
-// current one is converted: load_raw<TYPE> fetches the bytes, convert_raw<TYPE> turns them
-// into fp16.  Values follow the reference dequantisers (reference
+// Split in two: load_raw_s<TYPE> fetches the 32 weights' bytes from a copy of the super-block in
+// shared memory (the grouped GEMM stages raw blocks there with the TMA engine), load_raw<TYPE>
+// does the same from global memory, convert_raw<TYPE> turns them into fp16.  Values follow the reference dequantisers (reference
 // kernels/quant/kquant_matmul.cu:55-92,179-199, kernels/quant/iq2_matmul.cu:73-91):
 // d*sc*q - dmin*m, d*(sc-32)*q3, d*(0.5+ls)*0.25*grid*sign; Q4_K and IQ2_XXS are assembled
 // directly in fp16: the integer part is exact, the block scale is rounded to fp16 once.
@@ -22,18 +22,10 @@ __device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t *p) {  // 2-byte al
 // tables the converters read from shared memory
 struct DequantTables {
     const uint64_t *grid;   // IQ2_XXS codebook, 256 x 8 magnitudes
-    const uint4 *signs;     // 128 x 4 words: fp16 sign bits (15 and 31) of elements 2p, 2p+1 in word p
 };
 
-__device__ __forceinline__ void dequant_fill_tables(uint64_t *grid_s, uint4 *sign_s) {
+__device__ __forceinline__ void dequant_fill_tables(uint64_t *grid_s) {
     for (int i = threadIdx.x; i < 256; i += blockDim.x) grid_s[i] = k_iq2xxs_grid[i];
-    for (int i = threadIdx.x; i < 128; i += blockDim.x) {
-        const uint32_t sg = (uint32_t)i | ((uint32_t)(__popc(i) & 1) << 7);
-        uint32_t w[4];
-        for (int pp = 0; pp < 4; ++pp)
-            w[pp] = (((sg >> (2 * pp)) & 1u) << 15) | (((sg >> (2 * pp + 1)) & 1u) << 31);
-        sign_s[i] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
 }
 
 template <int TYPE> struct RawW;
@@ -87,6 +79,46 @@ __device__ __forceinline__ void load_raw<Q3_K>(const uint8_t *__restrict__ row, 
     }
 }
 
+// The same fields from a copy of the super-block in shared memory.  blk: shared address of the block's
+// first byte (alignment as in the tensor: 2, 4 or 16 bytes by type); kin: offset of the 32 weights inside
+// the super-block (multiple of 32).
+template <int TYPE>
+__device__ __forceinline__ void load_raw_s(uint32_t blk, int kin, RawW<TYPE> &r);
+
+template <>
+__device__ __forceinline__ void load_raw_s<IQ2_XXS>(uint32_t blk, int kin, RawW<IQ2_XXS> &r) {
+    uint32_t a[2];
+    lds32xN_any<2, 2>(blk + 2 + 8 * (kin >> 5), a);
+    r.aux0 = a[0]; r.aux1 = a[1];
+    r.d = lds16(blk);
+}
+template <>
+__device__ __forceinline__ void load_raw_s<Q4_K>(uint32_t blk, int kin, RawW<Q4_K> &r) {
+    const uint4 h = lds128(blk);
+    r.dd = h.x; r.s0 = h.y; r.s1 = h.z; r.s2 = h.w;
+    const int c = kin >> 6;
+    r.q0 = lds128(blk + 16 + 32 * c);
+    r.q1 = lds128(blk + 32 + 32 * c);
+}
+template <>
+__device__ __forceinline__ void load_raw_s<Q2_K>(uint32_t blk, int kin, RawW<Q2_K> &r) {
+    const int n = kin >> 7, j = (kin & 127) >> 5;
+    r.dd = lds32(blk + 80);
+    r.sc = lds16(blk + 8 * n + 2 * j);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r.w[i] = lds32(blk + 16 + 32 * n + 4 * i);
+}
+template <>
+__device__ __forceinline__ void load_raw_s<Q3_K>(uint32_t blk, int kin, RawW<Q3_K> &r) {
+    const int n = kin >> 7;
+    r.d = lds16(blk + 108);
+    uint32_t sc[3];
+    lds32xN_any<2, 3>(blk + 96, sc);
+    r.a0 = sc[0]; r.a1 = sc[1]; r.tmp = sc[2];
+    lds32xN_any<2, 8>(blk + 32 + 32 * n, r.q);
+    lds32xN_any<2, 8>(blk, r.hm);
+}
+
 __device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
 __device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
 
@@ -105,14 +137,20 @@ __device__ __forceinline__ void convert_raw<IQ2_XXS>(const RawW<IQ2_XXS> &r, int
 #pragma unroll
     for (int l = 0; l < 4; ++l) {
         const uint64_t g = tb.grid[(r.aux0 >> (8 * l)) & 255u];
-        const uint4 sg = tb.signs[(r.aux1 >> (7 * l)) & 127u];
+        // Sign bits of the eight elements: the seven stored ones and their parity (even number of minus
+        // signs per group of eight).  Bit 2p goes to bit 15 and bit 2p+1 to bit 31 of word p with one
+        // multiplication: s * (0x40008000 >> 2p) puts bit k of s at k + 15 - 2p and at k + 30 - 2p, the two
+        // ranges never overlap (no carries), and the mask keeps bits 15 and 31.  A table would cost a
+        // 16-byte shared-memory load with a random address per lane here.
+        const uint32_t s7 = (r.aux1 >> (7 * l)) & 127u;
+        const uint32_t s8 = s7 | ((__popc(s7) & 1u) << 7);
         const uint32_t glo = (uint32_t)g, ghi = (uint32_t)(g >> 32);
         const uint32_t ilo = (glo >> 4) & 0x03030303u, ihi = (ghi >> 4) & 0x03030303u;
         // selector for two elements: nibbles (2i0, 2i0+1, 2i1, 2i1+1) = 0x1010 + 0x22 * (i0 + 256 i1)
-        out[l].x = __byte_perm(t0, t1, 0x1010u + 0x22u * (ilo & 0xffffu)) ^ sg.x;
-        out[l].y = __byte_perm(t0, t1, 0x1010u + 0x22u * (ilo >> 16)) ^ sg.y;
-        out[l].z = __byte_perm(t0, t1, 0x1010u + 0x22u * (ihi & 0xffffu)) ^ sg.z;
-        out[l].w = __byte_perm(t0, t1, 0x1010u + 0x22u * (ihi >> 16)) ^ sg.w;
+        out[l].x = __byte_perm(t0, t1, 0x1010u + 0x22u * (ilo & 0xffffu)) ^ ((s8 * 0x40008000u) & 0x80008000u);
+        out[l].y = __byte_perm(t0, t1, 0x1010u + 0x22u * (ilo >> 16)) ^ ((s8 * 0x10002000u) & 0x80008000u);
+        out[l].z = __byte_perm(t0, t1, 0x1010u + 0x22u * (ihi & 0xffffu)) ^ ((s8 * 0x04000800u) & 0x80008000u);
+        out[l].w = __byte_perm(t0, t1, 0x1010u + 0x22u * (ihi >> 16)) ^ ((s8 * 0x01000200u) & 0x80008000u);
     }
 }
 

@@ -138,6 +138,22 @@ static int make_x_map(CUtensorMap *m, const void *base, int rows, int cols, int 
     return r == CUDA_SUCCESS ? ZMOE_OK : ZMOE_ERR_CUDA;
 }
 
+// quantised weights as bytes [E][O][rb], box = 128 rows x `pitch` bytes of one expert: the raw
+// super-blocks of a half tile in one copy.  Needs rows that are multiples of 16 bytes.
+static int make_w_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t expert_stride, int pitch) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return ZMOE_ERR_CUDA;
+    if (rb % 16 || expert_stride % 16 || pitch % 16 || pitch > 256) return ZMOE_ERR_SHAPE;
+    const cuuint64_t dims[3] = {(cuuint64_t)rb, (cuuint64_t)O, (cuuint64_t)E};
+    const cuuint64_t strides[2] = {(cuuint64_t)rb, (cuuint64_t)expert_stride};
+    const cuuint32_t box[3] = {(cuuint32_t)pitch, (cuuint32_t)GEMM_BM, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? ZMOE_OK : ZMOE_ERR_CUDA;
+}
+
 int make_rows_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t expert_stride, int R) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return ZMOE_ERR_CUDA;
@@ -163,22 +179,10 @@ int launch_gemm_sm100(const GemmLaunch &L, cudaStream_t st) {
     case IQ2_XXS: fn = L.dual ? gemm_sm100_kernel<IQ2_XXS, true> : gemm_sm100_kernel<IQ2_XXS, false>; break;
     default: return ZMOE_ERR_TYPE;
     }
-    const int stage = (L.dual ? 2 : 1) * GEMM_BM * GEMM_BK * 2 + GEMM_BN * GEMM_BK * 2;
-    const int nstage = L.dual ? 3 : 4;
-    const size_t smem = (size_t)nstage * stage + 1024;
-    {
-        static std::mutex mu;
-        static std::map<std::pair<const void *, int>, bool> done;
-        int dev = 0;
-        cudaGetDevice(&dev);
-        std::lock_guard<std::mutex> lock(mu);
-        bool &have = done[std::make_pair(reinterpret_cast<const void *>(fn), dev)];
-        if (!have) {
-            if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-                return ZMOE_ERR_CUDA;
-            have = true;
-        }
-    }
+    const int stage = 2 * GEMM_BM * GEMM_BK * 2 + GEMM_BN * GEMM_BK * 2;
+    const int pitch = gemm_raw_pitch(L.type);
+    const size_t smem = (size_t)GEMM_NSTAGE * stage + (size_t)GEMM_NRAW * 2 * GEMM_BM * pitch + 1024;
+    if (raise_dynamic_smem(reinterpret_cast<const void *>(fn), smem) != ZMOE_OK) return ZMOE_ERR_CUDA;
     GemmParams p;
     p.w0 = static_cast<const uint8_t *>(L.w0);
     p.w1 = static_cast<const uint8_t *>(L.w1);
@@ -189,10 +193,19 @@ int launch_gemm_sm100(const GemmLaunch &L, cudaStream_t st) {
     GemmMaps maps;
     for (int i = 0; i < 4; ++i)
         if (make_x_map(&maps.box[i], L.x_f16, L.x_rows, L.I, 32 << i)) return ZMOE_ERR_CUDA;
+    // raw super-blocks: one tiled copy per half tile where the rows allow it, else one bulk copy per row
+    p.raw_tiled = p.rb % 16 == 0 && L.stride0 % 16 == 0 && (!L.dual || L.stride1 % 16 == 0) && L.n_experts > 0;
+    if (p.raw_tiled) {
+        if (make_w_map(&maps.wmap[0], L.w0, L.n_experts, L.O, p.rb, L.stride0, pitch)) return ZMOE_ERR_CUDA;
+        if (make_w_map(&maps.wmap[1], L.dual ? L.w1 : L.w0, L.n_experts, L.O, p.rb, L.dual ? L.stride1 : L.stride0, pitch))
+            return ZMOE_ERR_CUDA;
+    } else {
+        maps.wmap[0] = maps.box[0];   // never read
+        maps.wmap[1] = maps.box[0];
+    }
     p.y = L.y; p.ldy = L.ldy;
     p.hdr = L.plan.hdr; p.active = L.plan.active; p.aoffs = L.plan.aoffs; p.antok = L.plan.antok; p.slot = L.plan.slot;
     p.clamp = L.clamp; p.clamp_fused = L.clamp_fused;
-    p.nstage = nstage;
     p.err = L.err;
     p.bad = L.dual ? L.bad : nullptr;
     return launch_pdl(fn, dim3(L.n_sm), dim3(GEMM_THREADS), smem, st, p, maps) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;

@@ -95,6 +95,7 @@ struct GemmLaunch {
     bool dual;
     const void *w0, *w1;
     size_t stride0, stride1;
+    int n_experts;         // experts the weight tensors hold
     int I, O;
     const void *x_f16;     // sorted activation rows [x_rows, I] fp16
     const float *xscale;   // their per-row scales
