@@ -138,6 +138,14 @@ def prefill_probe(lib, dev, seed, peaks, reps=5, E=E, T=4096):
            "tflops": tf, "bound": "tensor", "peak_tflops": peaks["bf16_tflops"], "frac": tf / peaks["bf16_tflops"],
            "pairs_per_expert": {"max": int(freq.max()), "median": float(np.median(freq)), "min": int(freq.min())},
            "kernel": "gemm_sm100_kernel (tcgen05.mma kind::f16, fp16 operands, f32 TMEM accumulators)"}
+    import ctypes as C
+    cyc = (C.c_uint64 * 32)()
+    if lib.load().zmoe_debug_gemm_cycles(cyc) == 0:      # only a profiling build of the library has them
+        names = ["stages", "conv_wait_raw", "conv_wait_stage", "conv_work", "conv_fence_arrive", "mma_wait_full",
+                 "mma_issue", "mma_wait_acc", "epi_wait", "epi_work", "load_wait", "load_issue", "tiles"]
+        n = 3 + reps       # calls since the counters were last cleared
+        res["gemm_cycles_cta0_per_call"] = {
+            k: {nm: cyc[16 * j + i] / n for i, nm in enumerate(names)} for j, k in enumerate(("gate_up", "down"))}
     del layer, ctx, wg, wu, wd
     torch.cuda.empty_cache()
     return res

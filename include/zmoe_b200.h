@@ -244,6 +244,11 @@ int zmoe_ctx_check(zmoe_ctx *ctx);
 int zmoe_ctx_bad_counts(zmoe_ctx *ctx, int32_t *counts_host, int clear);
 /* average pairs per expert from which zmoe_expert_ffn takes the tensor-core grouped GEMM when the path is 0 */
 int zmoe_gemm_min_pairs_per_expert(void);
+/* Profiling aid of the grouped GEMM.  A library built with -DZMOE_GEMM_STATS keeps per-role cycle sums of
+ * CTA 0 (waits and work of the converter, MMA, loader and epilogue warps; slots listed in
+ * csrc/gemm_sm100.cuh): this call waits for the device, copies the 2 x 16 counters (gate / up launches, then
+ * down launches) to counters32_host and clears them.  A normal build returns ZMOE_ERR_STATE and zeros. */
+int zmoe_debug_gemm_cycles(uint64_t *counters32_host);
 /* number of kernels this library has launched since load (all entry points) */
 uint64_t zmoe_kernel_launches(void);
 

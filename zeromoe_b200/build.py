@@ -41,6 +41,8 @@ def build(force=False, verbose=False):
     if not force and not _stale(LIB, deps):
         return LIB
     extra = ["-Xptxas", "-v"] if verbose else []
+    if os.environ.get("ZMOE_GEMM_STATS"):      # cycle accounting inside the grouped GEMM (a profiling build)
+        extra.append("-DZMOE_GEMM_STATS")
 
     def compile_one(src):
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))

@@ -48,6 +48,7 @@ struct PlanStore {
         rc |= dev_alloc(&b.freq, E);
         rc |= dev_alloc(&b.aoffs, E);
         rc |= dev_alloc(&b.antok, E);
+        rc |= dev_alloc(&b.pos, P);
         b.cap_e = E;
         cap_e = E;
         cap_p = P;
@@ -55,7 +56,7 @@ struct PlanStore {
     }
     void release() {
         cudaFree(b.hdr); cudaFree(b.active); cudaFree(b.offs); cudaFree(b.slot);
-        cudaFree(b.item_offs_gu); cudaFree(b.item_offs_dn); cudaFree(b.freq); cudaFree(b.aoffs); cudaFree(b.antok);
+        cudaFree(b.item_offs_gu); cudaFree(b.item_offs_dn); cudaFree(b.freq); cudaFree(b.aoffs); cudaFree(b.antok); cudaFree(b.pos);
         b = PlanBuffers();
         cap_e = cap_p = 0;
     }
@@ -117,6 +118,8 @@ struct zmoe_ctx {
     int path = 0;              // 0 auto, 1 decode kernels, 2 tensor-core GEMM, 3 decode kernels, scalar path only
     float *ydown = nullptr;    // [P, D] per-pair down-projection output
     float *logits = nullptr;   // [T, E] router logits, then probabilities
+    float *logits_part = nullptr;  // [ROUTER_MAX_SPLIT][T, E] partial logits of the large-batch router (contexts of > 256 tokens)
+    bool q8x_valid = false;    // q8x (and q8x2) hold the quantised rows of x_last
     int32_t *ids = nullptr;    // [T, K]
     float *weights = nullptr;  // [T, K]
     PlanStore plan;
@@ -165,6 +168,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     rc |= dev_alloc(&c->actscale, P);
     rc |= dev_alloc(&c->ydown, P * max_d_model);
     rc |= dev_alloc(&c->logits, (size_t)max_tokens * max_experts);
+    if (max_tokens > 256) rc |= dev_alloc(&c->logits_part, (size_t)ROUTER_MAX_SPLIT * max_tokens * max_experts);
     rc |= dev_alloc(&c->ids, P);
     rc |= dev_alloc(&c->weights, P);
     rc |= c->plan.alloc(max_experts, (int)P);
@@ -205,7 +209,7 @@ void zmoe_ctx_destroy(zmoe_ctx *c) {
     cudaFree(c->zero_ids); cudaFree(c->one_w);
     cudaFree(c->xq_f16); cudaFree(c->actq_f16); cudaFree(c->xscale); cudaFree(c->actscale);
     cudaFree(c->q8x); cudaFree(c->q8x2); cudaFree(c->act); cudaFree(c->act2); cudaFree(c->q8act); cudaFree(c->ydown);
-    cudaFree(c->logits); cudaFree(c->ids); cudaFree(c->weights); cudaFree(c->err); cudaFree(c->bad); cudaFree(c->ticket);
+    cudaFree(c->logits); cudaFree(c->logits_part); cudaFree(c->ids); cudaFree(c->weights); cudaFree(c->err); cudaFree(c->bad); cudaFree(c->ticket);
     cudaFree(c->x_stage); cudaFree(c->out_stage);
     c->plan.release();
     if (c->host_stream) cudaStreamDestroy(c->host_stream);
@@ -268,6 +272,30 @@ int zmoe_layer_create(zmoe_ctx *ctx, const zmoe_layer_desc *desc, zmoe_layer **o
 
 void zmoe_layer_destroy(zmoe_layer *layer) { delete layer; }
 
+// whether zmoe_expert_ffn will take the tensor-core grouped GEMM for T tokens (the rule of the header:
+// shapes allow it, and the path is forced to 2 or left at 0 with enough pairs per expert)
+static bool takes_gemm(const zmoe_layer *L, int T) {
+    const zmoe_layer_desc &d = L->d;
+    const zmoe_ctx *c = L->ctx;
+    const bool gemm_ok = L->dual && gemm_sm100_supported(d.gate.type, d.d_model, d.d_ff) &&
+                         gemm_sm100_supported(d.down.type, d.d_ff, d.d_model) && d.n_experts <= 512;
+    const long P = (long)T * d.topk;
+    return gemm_ok && (c->path == 2 || (c->path == 0 && P >= (long)kGemmMinPairsPerExpert * d.n_experts));
+}
+
+// packed Q8_K rows of the layer input for the decode kernels (both unit layouts where gate and up differ)
+static int quantize_input(zmoe_layer *L, const float *x_dev, int T, cudaStream_t st) {
+    zmoe_ctx *c = L->ctx;
+    int rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x, T, L->d.d_model, q8_layout_of(L->d.gate.type), st);
+    g_launches += 1;
+    if (!rc && q8_layout_of(L->d.up.type) != q8_layout_of(L->d.gate.type)) {
+        rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x2, T, L->d.d_model, q8_layout_of(L->d.up.type), st);
+        g_launches += 1;
+    }
+    if (!rc) c->q8x_valid = true;
+    return rc;
+}
+
 int zmoe_route(zmoe_layer *L, const float *x_dev, int T, void *stream) {
     if (!L || !x_dev || T <= 0) return ZMOE_ERR_ARG;
     zmoe_ctx *c = L->ctx;
@@ -284,13 +312,18 @@ int zmoe_route(zmoe_layer *L, const float *x_dev, int T, void *stream) {
     a.plan = c->plan.b;
     a.nrt_gu = L->nrt_gu; a.nrt_dn = L->nrt_dn;
     a.ticket = c->ticket;
+    a.logits_part = c->logits_part;
+    a.n_sm = c->n_sm;
     // one CTA per (expert, 4 tokens) re-reads every activation row E times: fine up to a few hundred
     // tokens (the tiled GEMM has only (E / 64) x (T / 64) CTAs: 4 at 128 tokens, 280 us per call)
     const bool big = T > 256;
+    // the tensor-core path quantises the rows itself while it gathers them: the large-batch router then skips q8x
+    a.want_q8x = !(big && takes_gemm(L, T));
     int rc = big ? launch_router_prefill(a, static_cast<cudaStream_t>(stream))
                  : launch_router_decode(a, static_cast<cudaStream_t>(stream));
-    g_launches += big ? 4 : 1;
-    if (!rc && q8_layout_of(L->d.up.type) != a.q8_layout) {
+    g_launches += big ? (a.want_q8x ? 4 : 3) : 1;
+    c->q8x_valid = a.want_q8x;
+    if (!rc && a.want_q8x && q8_layout_of(L->d.up.type) != a.q8_layout) {
         rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x2, T, L->d.d_model, q8_layout_of(L->d.up.type),
                                   static_cast<cudaStream_t>(stream));
         g_launches += 1;
@@ -306,16 +339,14 @@ static int set_routes_impl(zmoe_layer *L, const float *x_dev, const int32_t *ids
     if (T > c->max_t) return ZMOE_ERR_CAPACITY;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t P = (size_t)T * L->d.topk;
-    int rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x, T, L->d.d_model, q8_layout_of(L->d.gate.type), st);
-    if (!rc && q8_layout_of(L->d.up.type) != q8_layout_of(L->d.gate.type)) {
-        rc = launch_quantize_rows(x_dev, L->d.d_model, c->q8x2, T, L->d.d_model, q8_layout_of(L->d.up.type), st);
-        g_launches += 1;
-    }
+    int rc = 0;
+    c->q8x_valid = false;
+    if (!takes_gemm(L, T)) rc = quantize_input(L, x_dev, T, st);   // the tensor-core path quantises while it gathers
     // the planner takes the routes in (copy, window mapping) before it groups them: one launch
     if (!rc)
         rc = launch_plan_ingest(ids_dev, weights_dev, c->ids, c->weights, (int)P, L->d.n_experts, first_expert, window,
                                 c->plan.b, L->nrt_gu, L->nrt_dn, st);
-    if (!rc) { g_launches += 2; c->routed_t = T; c->x_last = x_dev; }
+    if (!rc) { g_launches += 1; c->routed_t = T; c->x_last = x_dev; }
     return rc;
 }
 
@@ -352,16 +383,14 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
     m.multi = T > 1 && c->path != 3;
     int rc;
     // many pairs per expert: the contraction is compute-bound and goes to the tensor cores
-    const bool gemm_ok = L->dual && c->x_last && gemm_sm100_supported(d.gate.type, d.d_model, d.d_ff) &&
-                         gemm_sm100_supported(d.down.type, d.d_ff, d.d_model) && d.n_experts <= 512;
-    const bool use_gemm = gemm_ok && (c->path == 2 || (c->path == 0 && (long)P >= (long)kGemmMinPairsPerExpert * d.n_experts));
+    const bool use_gemm = c->x_last && takes_gemm(L, T);
     if (use_gemm) {
         if (ev_before) cudaEventRecord(static_cast<cudaEvent_t>(ev_before), st);
         GemmLaunch g;
         g.plan = c->plan.b; g.err = c->err; g.bad = c->bad; g.n_sm = c->n_sm;
         g.clamp = d.swiglu_clamp; g.clamp_fused = d.swiglu_clamp_fused;
         g.n_experts = d.n_experts;
-        rc = launch_q8_roundtrip_f16(c->x_last, d.d_model, c->xq_f16, c->xscale, c->plan.b, P, d.topk, d.d_model, st);
+        rc = launch_q8_roundtrip_tokens_f16(c->x_last, d.d_model, c->xq_f16, c->xscale, c->plan.b, T, d.topk, d.d_model, st);
         g.type = d.gate.type; g.dual = true;
         g.w0 = d.gate.data_dev; g.w1 = d.up.data_dev;
         g.stride0 = d.gate.expert_stride; g.stride1 = d.up.expert_stride;
@@ -381,6 +410,12 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         if (!rc) rc = launch_combine(out_dev, c->ydown, c->weights, c->ids, T, d.topk, d.d_model, d.n_experts, accumulate, st);
         g_launches += 5;
         return rc;
+    }
+    // the path may have been changed since the routes were set: the decode kernels need the quantised input
+    if (!c->q8x_valid) {
+        if (!c->x_last) return ZMOE_ERR_STATE;
+        rc = quantize_input(L, c->x_last, T, st);
+        if (rc) return rc;
     }
     if (ev_before) cudaEventRecord(static_cast<cudaEvent_t>(ev_before), st);
     if (L->dual) {
@@ -522,6 +557,12 @@ int zmoe_ctx_bad_counts(zmoe_ctx *c, int32_t *counts_host, int clear) {
 }
 
 int zmoe_gemm_min_pairs_per_expert(void) { return kGemmMinPairsPerExpert; }
+
+int zmoe_debug_gemm_cycles(uint64_t *counters32_host) {
+    if (!counters32_host) return ZMOE_ERR_ARG;
+    if (cudaDeviceSynchronize() != cudaSuccess) return ZMOE_ERR_CUDA;
+    return gemm_stats_read(reinterpret_cast<unsigned long long *>(counters32_host));
+}
 
 uint64_t zmoe_kernel_launches(void) { return g_launches.load(); }
 

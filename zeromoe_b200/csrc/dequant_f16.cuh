@@ -21,11 +21,22 @@ __device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t *p) {  // 2-byte al
 
 // tables the converters read from shared memory
 struct DequantTables {
-    const uint64_t *grid;   // IQ2_XXS codebook, 256 x 8 magnitudes
+    uint32_t grid;   // shared address of the IQ2_XXS selector table: 256 x 8 bytes
 };
 
-__device__ __forceinline__ void dequant_fill_tables(uint64_t *grid_s) {
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) grid_s[i] = k_iq2xxs_grid[i];
+// Entry e of the table: four 16-bit byte-permute selectors, one per pair of elements (2p, 2p+1).  With
+// i0, i1 the codes (0, 1, 2 for the magnitudes 8, 25, 43: their high nibbles) of the two elements, the
+// selector's nibbles are (2 i0, 2 i0 + 1, 2 i1, 2 i1 + 1): the two bytes of each fp16 table entry.
+__device__ __forceinline__ void dequant_fill_tables(uint2 *grid_s) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        const uint64_t g = k_iq2xxs_grid[i];
+        uint32_t w[4];
+        for (int pp = 0; pp < 4; ++pp) {
+            const uint32_t i0 = (uint32_t)(g >> (16 * pp + 4)) & 3u, i1 = (uint32_t)(g >> (16 * pp + 12)) & 3u;
+            w[pp] = 0x1010u + 0x22u * (i0 + 256u * i1);
+        }
+        grid_s[i] = make_uint2(w[0] | (w[1] << 16), w[2] | (w[3] << 16));
+    }
 }
 
 template <int TYPE> struct RawW;
@@ -125,9 +136,11 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cas
 template <int TYPE>
 __device__ __forceinline__ void convert_raw(const RawW<TYPE> &r, int k0, const DequantTables &tb, uint4 (&out)[4]);
 
-// IQ2_XXS: the codebook holds only the magnitudes 8, 25 and 43, whose high nibbles 0, 1, 2 index
-// a three-entry fp16 table kept in a register pair; byte permutes assemble the values, the sign
-// table supplies the sign bits.
+// IQ2_XXS: the codebook holds only the magnitudes 8, 25 and 43, which index a three-entry fp16 table
+// (the magnitudes times the sub-block scale) kept in a register pair; one byte permute per pair of
+// elements assembles the values.  The shared-memory copy of the codebook holds, per entry, the four
+// ready-made permute selectors (16 bits each) instead of the magnitudes: the converters are bound by
+// instruction issue, and this takes the selector arithmetic out of the loop.
 template <>
 __device__ __forceinline__ void convert_raw<IQ2_XXS>(const RawW<IQ2_XXS> &r, int k0, const DequantTables &tb,
                                                      uint4 (&out)[4]) {
@@ -136,21 +149,18 @@ __device__ __forceinline__ void convert_raw<IQ2_XXS>(const RawW<IQ2_XXS> &r, int
     const uint32_t t1 = h2_bits(__floats2half2_rn(db * 43.f, 0.f));        // entry 2
 #pragma unroll
     for (int l = 0; l < 4; ++l) {
-        const uint64_t g = tb.grid[(r.aux0 >> (8 * l)) & 255u];
+        const uint2 sel = lds64(tb.grid + 8 * ((r.aux0 >> (8 * l)) & 255u));
         // Sign bits of the eight elements: the seven stored ones and their parity (even number of minus
         // signs per group of eight).  Bit 2p goes to bit 15 and bit 2p+1 to bit 31 of word p with one
         // multiplication: s * (0x40008000 >> 2p) puts bit k of s at k + 15 - 2p and at k + 30 - 2p, the two
-        // ranges never overlap (no carries), and the mask keeps bits 15 and 31.  A table would cost a
-        // 16-byte shared-memory load with a random address per lane here.
+        // ranges never overlap (no carries), and the mask keeps bits 15 and 31.
         const uint32_t s7 = (r.aux1 >> (7 * l)) & 127u;
         const uint32_t s8 = s7 | ((__popc(s7) & 1u) << 7);
-        const uint32_t glo = (uint32_t)g, ghi = (uint32_t)(g >> 32);
-        const uint32_t ilo = (glo >> 4) & 0x03030303u, ihi = (ghi >> 4) & 0x03030303u;
-        // selector for two elements: nibbles (2i0, 2i0+1, 2i1, 2i1+1) = 0x1010 + 0x22 * (i0 + 256 i1)
-        out[l].x = __byte_perm(t0, t1, 0x1010u + 0x22u * (ilo & 0xffffu)) ^ ((s8 * 0x40008000u) & 0x80008000u);
-        out[l].y = __byte_perm(t0, t1, 0x1010u + 0x22u * (ilo >> 16)) ^ ((s8 * 0x10002000u) & 0x80008000u);
-        out[l].z = __byte_perm(t0, t1, 0x1010u + 0x22u * (ihi & 0xffffu)) ^ ((s8 * 0x04000800u) & 0x80008000u);
-        out[l].w = __byte_perm(t0, t1, 0x1010u + 0x22u * (ihi >> 16)) ^ ((s8 * 0x01000200u) & 0x80008000u);
+        // the permute reads only the low 16 bits of its selector
+        out[l].x = __byte_perm(t0, t1, sel.x) ^ ((s8 * 0x40008000u) & 0x80008000u);
+        out[l].y = __byte_perm(t0, t1, sel.x >> 16) ^ ((s8 * 0x10002000u) & 0x80008000u);
+        out[l].z = __byte_perm(t0, t1, sel.y) ^ ((s8 * 0x04000800u) & 0x80008000u);
+        out[l].w = __byte_perm(t0, t1, sel.y >> 16) ^ ((s8 * 0x01000200u) & 0x80008000u);
     }
 }
 

@@ -10,9 +10,10 @@
 // against up to 256 pairs; both halves multiply the same activation tile, which halves the
 // activation traffic per flop.
 //   warp 17    loader: copies the raw quantised super-blocks of the tile's 256 rows, one
-//              super-block column (256 k) at a time, into a two-slot ring in shared memory with the
-//              TMA engine (one tiled copy per 128 rows where rows are multiples of 16 bytes, else
-//              one bulk copy per row; no multicast), completion on mbarriers.
+//              super-block column (256 k) at a time, into a two-slot ring in shared memory with
+//              tiled copies on the TMA engine (no multicast), completion on mbarriers.  Rows that are
+//              not multiples of 16 bytes are addressed G rows at a time (G * row bytes is one): G
+//              copies per 128 rows, one per position of a row inside its group.
 //   warps 0-15 converters: read the raw blocks from shared memory and write them as fp16 in the
 //              128-byte-swizzled K-major layout tcgen05 reads, 64 k per pipeline stage; one of
 //              them issues the tiled copy of the matching 64-k slice of the activation rows,
@@ -62,7 +63,7 @@ struct GemmParams {
     size_t stride0, stride1;     // bytes between experts
     int I, O;                    // k extent, weight rows per expert (multiple of 128)
     int rb;                      // bytes per weight row
-    int raw_tiled;               // raw blocks come through the tiled maps wmap[] (rows are multiples of 16 bytes)
+    int g_log2;                  // log2 of G, the rows per group whose bytes are a multiple of 16 (1, 2, 4 or 8 rows)
     const float *xscale;         // per SORTED activation row: the power of two the row was divided by
     float *y;                    // output [pair][ldy]
     int ldy;
@@ -71,11 +72,30 @@ struct GemmParams {
     int clamp_fused;
     int *err;
     int *bad;                    // DUAL: [2] counters of NaN / Inf gate or up values, or null
+    unsigned long long *stats;   // cycle counters of CTA 0's roles (builds with ZMOE_GEMM_STATS only), or null
 };
+
+// Cycle accounting of one CTA's roles, compiled in with -DZMOE_GEMM_STATS (python -m zeromoe_b200.build with
+// ZMOE_GEMM_STATS=1 in the environment): one thread per role of CTA 0 adds up clock64() differences around
+// its waits and its work and stores the sums when the kernel ends.  Slots: 0 stages converted, 1 converter
+// wait for raw blocks, 2 converter wait for a free stage, 3 load + convert + store, 4 fence + arrive,
+// 5 MMA wait for a full stage, 6 MMA issue + commit, 7 MMA wait for the accumulators, 8 epilogue wait,
+// 9 epilogue work, 10 loader wait for a free slot, 11 loader issue, 12 tiles.
+#ifdef ZMOE_GEMM_STATS
+#define GSTAT_DECL unsigned long long gs_t0 = 0, gs_acc[4] = {0, 0, 0, 0}; const bool gs_on = blockIdx.x == 0 && p.stats != nullptr
+#define GSTAT_BEGIN() do { if (gs_on) gs_t0 = clock64(); } while (0)
+#define GSTAT_END(i) do { if (gs_on) { const unsigned long long gs_t1 = clock64(); gs_acc[i] += gs_t1 - gs_t0; gs_t0 = gs_t1; } } while (0)
+#define GSTAT_STORE(i, slot) do { if (gs_on) p.stats[slot] += gs_acc[i]; } while (0)
+#else
+#define GSTAT_DECL do { } while (0)
+#define GSTAT_BEGIN() do { } while (0)
+#define GSTAT_END(i) do { } while (0)
+#define GSTAT_STORE(i, slot) do { } while (0)
+#endif
 
 // Activation tile maps with boxes of 32, 64, 128 and 256 rows (a tile loads the smallest box that covers
 // its pairs, so an expert with few pairs does not pull 256 rows through L2 for every k-step) and the
-// byte maps [E][O][rb] of the weight tensors with a box of 128 rows x one raw row pitch.
+// byte maps [E][O / G][G * rb] of the weight tensors with a box of 128 / G row groups x one raw row pitch.
 struct GemmMaps {
     alignas(64) CUtensorMap box[4];
     alignas(64) CUtensorMap wmap[2];
@@ -97,7 +117,7 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
         raw_empty[GEMM_NRAW], acc_full, acc_empty;
     __shared__ uint32_t tmem_slot;
     __shared__ int s_tile_offs[GEMM_MAX_ACTIVE + 1];
-    __shared__ __align__(16) uint64_t grid_s[TYPE == IQ2_XXS ? 256 : 2];
+    __shared__ __align__(16) uint2 grid_s[TYPE == IQ2_XXS ? 256 : 2];
 
     // 1024-byte alignment of the operand tiles (required by the 128-byte swizzle)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -127,7 +147,7 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
     }
     if (warp == GEMM_CWARPS) tmem_alloc(&tmem_slot, TMEM_COLS);
     if (TYPE == IQ2_XXS) dequant_fill_tables(grid_s);
-    const DequantTables tb{grid_s};
+    const DequantTables tb{smem_u32(grid_s)};
 
     pdl_wait_prior_grid();
     pdl_launch_dependents();
@@ -171,11 +191,6 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
         p0 = p.aoffs[lo] + nb * bsz;
         np = max(0, min(bsz, cnt - nb * bsz));
     };
-    // first byte of row r (0..127) of half h of the tile in global memory
-    auto half_row = [&](int h, int e, int m0, int r) -> const uint8_t * {
-        if (DUAL) return (h ? p.w1 + (size_t)e * p.stride1 : p.w0 + (size_t)e * p.stride0) + (size_t)(m0 + r) * p.rb;
-        return p.w0 + (size_t)e * p.stride0 + (size_t)(m0 + GEMM_BM * h + r) * p.rb;
-    };
     // the second half of a tile exists unless the matrix ends after the first (rows a multiple of 128, not 256)
     auto has_half1 = [&](int m0) -> bool { return DUAL || m0 + GEMM_BM < p.O; };
 
@@ -185,31 +200,41 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
         int rc = 0;   // raw slot use counter
         // thread -> (half tile, row r, 32-k half of the stage)
         const int which = tid >> 8, r = (tid & 255) >> 1, half = tid & 1;
+        // where this thread's four 16-byte chunks go inside a stage (fixed for the whole kernel)
+        const uint32_t stage0 = smem_u32(smem);
+        uint32_t st_off[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) st_off[c] = which * A_BYTES + swz128_offset(r, 32 * half + 8 * c);
+        GSTAT_DECL;
         for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
             int e, m0, p0, np;
             tile_info(tile, e, m0, p0, np);
             const int ncols = (np + 15) & ~15;
             const bool worker = which == 0 || has_half1(m0);
-            const uint8_t *grow = half_row(which, e, m0, r);
             uint32_t blk = 0;
             for (int ks = 0; ks < ksteps; ++ks, ++it) {
                 const int s = it % GEMM_NSTAGE;
                 const int rs = rc % GEMM_NRAW;
+                GSTAT_BEGIN();
                 if ((ks & 3) == 0) {
                     // a new super-block column: its raw copy must have landed
-                    if (!mbar_wait(&raw_full[rs], (rc / GEMM_NRAW) & 1)) {
+                    if (!mbar_wait_suspend(&raw_full[rs], (rc / GEMM_NRAW) & 1)) {
                         atomicExch(p.err, 7);
                         alive = false;
                         break;
                     }
-                    const uint32_t off = (uint32_t)(reinterpret_cast<uintptr_t>(grow + (size_t)(ks >> 2) * BB) & 15u);
-                    blk = smem_u32(raw_base) + rs * RAW_SLOT + which * RAW_HALF + r * PITCH + off;
+                    // row r = G * sr + j sits in sub-array j (the copy of position j of every group) at sr
+                    const int G = 1 << p.g_log2, j = r & (G - 1), sr = r >> p.g_log2;
+                    const uint32_t off = (uint32_t)(j * p.rb + (ks >> 2) * BB) & 15u;
+                    blk = smem_u32(raw_base) + rs * RAW_SLOT + which * RAW_HALF + (j * (GEMM_BM >> p.g_log2) + sr) * PITCH + off;
                 }
-                if (it >= GEMM_NSTAGE && !mbar_wait(&empty_bar[s], ((it / GEMM_NSTAGE) - 1) & 1)) {
+                GSTAT_END(0);
+                if (it >= GEMM_NSTAGE && !mbar_wait_suspend(&empty_bar[s], ((it / GEMM_NSTAGE) - 1) & 1)) {
                     atomicExch(p.err, 3);
                     alive = false;
                     break;
                 }
+                GSTAT_END(1);
                 uint8_t *stage = smem + (size_t)s * STAGE_BYTES;
                 const int k0 = ks * GEMM_BK;
                 if (tid == 0) {
@@ -224,11 +249,11 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
                     load_raw_s<TYPE>(blk, (k0 & 255) + 32 * half, raw);
                     uint4 a[4];
                     convert_raw<TYPE>(raw, k0 + 32 * half, tb, a);
-                    uint8_t *tile_s = stage + which * A_BYTES;
+                    const uint32_t sbase = stage0 + s * STAGE_BYTES;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        *reinterpret_cast<uint4 *>(tile_s + swz128_offset(r, 32 * half + 8 * c)) = a[c];
+                    for (int c = 0; c < 4; ++c) sts128(sbase + st_off[c], a[c]);
                 }
+                GSTAT_END(2);
                 fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) {
@@ -236,8 +261,15 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
                     if ((ks & 3) == 3) mbar_arrive(&raw_empty[rs]);   // this warp is done with the raw slot
                 }
                 if ((ks & 3) == 3) ++rc;
+                GSTAT_END(3);
             }
         }
+#ifdef ZMOE_GEMM_STATS
+        if (tid == 32) {
+            if (gs_on) p.stats[0] += (unsigned long long)it;
+            GSTAT_STORE(0, 1); GSTAT_STORE(1, 2); GSTAT_STORE(2, 3); GSTAT_STORE(3, 4);
+        }
+#endif
     } else if (warp == GEMM_CWARPS) {
         // ------------------------------- MMA issuer ------------------------------------
         int it = 0, nt = 0;
@@ -246,26 +278,31 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
         const uint32_t sa0 = smem_u32(smem), sa1 = sa0 + STAGE_BYTES;
         const uint64_t d0a0 = umma_desc_sw128(sa0), d0a1 = umma_desc_sw128(sa0 + A_BYTES), d0b = umma_desc_sw128(sa0 + 2 * A_BYTES);
         const uint64_t d1a0 = umma_desc_sw128(sa1), d1a1 = umma_desc_sw128(sa1 + A_BYTES), d1b = umma_desc_sw128(sa1 + 2 * A_BYTES);
+        GSTAT_DECL;
         for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++nt) {
             int e, m0, p0, np;
             tile_info(tile, e, m0, p0, np);
             const int ncols = (np + 15) & ~15;
             const uint32_t idesc = umma_idesc_f16(GEMM_BM, ncols);
             const bool two = has_half1(m0);
+            GSTAT_BEGIN();
             // the epilogue must have drained the previous tile's accumulators
-            if (nt >= 1 && !mbar_wait_sleep(&acc_empty, (nt - 1) & 1, 64)) {
+            if (nt >= 1 && !mbar_wait_suspend(&acc_empty, (nt - 1) & 1)) {
                 if (lane == 0) atomicExch(p.err, 4);
                 alive = false;
                 break;
             }
+            GSTAT_END(2);
             tc_fence_after_sync();
             for (int ks = 0; ks < ksteps; ++ks, ++it) {
                 const int s = it % GEMM_NSTAGE;
-                if (!mbar_wait(&full_bar[s], (it / GEMM_NSTAGE) & 1, 1u << 22)) {
+                GSTAT_BEGIN();
+                if (!mbar_wait_suspend(&full_bar[s], (it / GEMM_NSTAGE) & 1)) {
                     if (lane == 0) atomicExch(p.err, 5);
                     alive = false;
                     break;
                 }
+                GSTAT_END(0);
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint64_t a0 = s ? d1a0 : d0a0, a1 = s ? d1a1 : d0a1, b0 = s ? d1b : d0b;
@@ -278,69 +315,76 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
                     if (ks == ksteps - 1) umma_commit(&acc_full);  // accumulators complete
                 }
                 __syncwarp();
+                GSTAT_END(1);
             }
         }
+#ifdef ZMOE_GEMM_STATS
+        if (lane == 0) { GSTAT_STORE(0, 5); GSTAT_STORE(1, 6); GSTAT_STORE(2, 7); if (gs_on) p.stats[12] += (unsigned long long)nt; }
+#endif
     } else if (warp == GEMM_CWARPS + 1) {
         // ------------------------------- raw loader ------------------------------------
         int rc = 0;
+        GSTAT_DECL;
         for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
             int e, m0, p0, np;
             tile_info(tile, e, m0, p0, np);
             const bool two = has_half1(m0);
             for (int b = 0; b < nblk; ++b, ++rc) {
                 const int rs = rc % GEMM_NRAW;
-                if (rc >= GEMM_NRAW && !mbar_wait_sleep(&raw_empty[rs], ((rc / GEMM_NRAW) - 1) & 1, 32, 1u << 20)) {
+                GSTAT_BEGIN();
+                if (rc >= GEMM_NRAW && !mbar_wait_suspend(&raw_empty[rs], ((rc / GEMM_NRAW) - 1) & 1)) {
                     if (lane == 0) atomicExch(p.err, 8);
                     alive = false;
                     break;
                 }
+                GSTAT_END(0);
                 const uint32_t dst = smem_u32(raw_base) + rs * RAW_SLOT;
-                if (p.raw_tiled) {
-                    // rows are multiples of 16 bytes: every row's block starts at the same offset from a
-                    // 16-byte boundary; one box of 128 rows x PITCH bytes per half tile (bytes past the
-                    // end of a row arrive as zeros and are never read)
-                    if (lane == 0) {
-                        const int x = (b * BB) & ~15;
-                        mbar_arrive_expect_tx(&raw_full[rs], (uint32_t)((two ? 2 : 1) * RAW_HALF));
-                        tma_load_3d(dst, &maps.wmap[0], x, m0, e, &raw_full[rs]);
-                        if (two) tma_load_3d(dst + RAW_HALF, &maps.wmap[DUAL ? 1 : 0], x, DUAL ? m0 : m0 + GEMM_BM, e, &raw_full[rs]);
-                    }
-                } else {
-                    // one bulk copy per row, from the 16-byte boundary at or below the block's first byte
-                    // to the one at or above its last (the tensor ends on such a boundary)
-                    uint32_t bytes = 0;
-#pragma unroll 4
-                    for (int i = 0; i < 8; ++i) {
-                        const int idx = lane + 32 * i, h = idx >> 7, r = idx & 127;
-                        if (h == 0 || two) {
-                            const uint8_t *src = half_row(h, e, m0, r) + (size_t)b * BB;
-                            const uint32_t off = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15u);
-                            const uint32_t sz = (off + BB + 15u) & ~15u;
-                            bulk_g2s_addr(dst + h * RAW_HALF + r * PITCH, src - off, sz, &raw_full[rs]);
-                            bytes += sz;
-                        }
-                    }
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
-                    // the copies above cannot complete the phase before this arrival registers their bytes
-                    if (lane == 0) mbar_arrive_expect_tx(&raw_full[rs], bytes);
+                // G tiled copies per half tile: copy j brings, for each of the 128 / G row groups, the window
+                // of PITCH bytes that holds block b of the group's row j (it starts on the 16-byte boundary at or
+                // below the block; bytes past the end of a group arrive as zeros and are never read)
+                const int G = 1 << p.g_log2;
+                if (lane == 0) mbar_arrive_expect_tx(&raw_full[rs], (uint32_t)((two ? 2 : 1) * RAW_HALF));
+                __syncwarp();
+                if (lane < 2 * G && (lane < G || two)) {
+                    const int h = lane >= G, j = lane & (G - 1);
+                    const int x = (j * p.rb + b * BB) & ~15;
+                    const int row0 = (DUAL || h == 0) ? m0 : m0 + GEMM_BM;
+                    tma_load_3d(dst + h * RAW_HALF + j * (GEMM_BM >> p.g_log2) * PITCH, &maps.wmap[DUAL ? h : 0], x,
+                                row0 >> p.g_log2, e, &raw_full[rs]);
                 }
                 __syncwarp();
+                GSTAT_END(1);
             }
         }
+#ifdef ZMOE_GEMM_STATS
+        if (lane == 0) { GSTAT_STORE(0, 10); GSTAT_STORE(1, 11); }
+#endif
     } else {
         // ------------------------------- epilogue --------------------------------------
         const int q = warp & 3;              // the warp's quarter of the 128 tensor-memory lanes
         int nt = 0;
+        GSTAT_DECL;
         for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++nt) {
             int e, m0, p0, np;
             tile_info(tile, e, m0, p0, np);
             const bool two = has_half1(m0);
-            if (!mbar_wait_sleep(&acc_full, nt & 1, 256)) {
+            // pair ids and scales of the tile's columns, lane j of chunk c holding column 32 c + j: fetched now,
+            // while the tile's MMAs are still running
+            int mp[GEMM_BN / 32];
+            float ms[GEMM_BN / 32];
+#pragma unroll
+            for (int c = 0; c < GEMM_BN / 32; ++c) {
+                const int col = 32 * c + lane;
+                mp[c] = col < np ? p.slot[p0 + col] : -1;
+                ms[c] = col < np ? p.xscale[p0 + col] : 0.f;
+            }
+            GSTAT_BEGIN();
+            if (!mbar_wait_suspend(&acc_full, nt & 1)) {
                 if (lane == 0) atomicExch(p.err, 6);
                 alive = false;
                 break;
             }
+            GSTAT_END(0);
             tc_fence_after_sync();
             const int f = m0 + 32 * q + lane;   // this thread's weight row (first half)
             const uint32_t tl = tmem_base + ((uint32_t)(32 * q) << 16);
@@ -348,32 +392,57 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
                 uint32_t g[32], u[32];
                 tmem_ld_32x32(tl + c0, g);
                 if (two) tmem_ld_32x32(tl + GEMM_BN + c0, u);
-                // column metadata: lane j fetches pair id and scale of column c0 + j once, the loop
-                // below broadcasts them (32 dependent scalar loads per chunk would serialise on latency)
-                const int my_pair = c0 + lane < np ? p.slot[p0 + c0 + lane] : 0;
-                const float my_sc = c0 + lane < np ? p.xscale[p0 + c0 + lane] : 0.f;
+                // column metadata (fetched before the wait for the accumulators): lane j holds pair id and
+                // scale of column c0 + j, the loops below broadcast them
+                const int my_pair = mp[c0 >> 5];
+                const float my_sc = ms[c0 >> 5];
                 tmem_ld_wait();
+                // the arithmetic of all 32 columns first, without branches, so that the columns' dependency
+                // chains interleave (one warp per scheduler does this while the tensor memory is held);
+                // x - x is 0 for a finite x and NaN otherwise: the sum flags a non-finite gate / up value
+                float probe = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float sc = __shfl_sync(0xffffffffu, my_sc, j);
+                    const float gv = __uint_as_float(g[j]) * sc;
+                    if (DUAL) {
+                        const float uv = __uint_as_float(u[j]) * sc;
+                        probe += (gv - gv) + (uv - uv);
+                        g[j] = __float_as_uint(swiglu_fast(gv, uv, p.clamp, p.clamp_fused));
+                    } else {
+                        g[j] = __float_as_uint(gv);
+                        if (two) u[j] = __float_as_uint(__uint_as_float(u[j]) * sc);
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int pair = __shfl_sync(0xffffffffu, my_pair, j);
-                    const float sc = __shfl_sync(0xffffffffu, my_sc, j);
-                    if (c0 + j < np) {
-                        const float v = __uint_as_float(g[j]) * sc;
+                    if (pair >= 0) {
                         float *row = p.y + (size_t)pair * p.ldy;
-                        if (DUAL) {
-                            const float uv = __uint_as_float(u[j]) * sc;
-                            count_bad(p.bad, v, uv);
-                            row[f] = swiglu_f(v, uv, p.clamp, p.clamp_fused);
-                        } else {
-                            row[f] = v;
-                            if (two) row[f + GEMM_BM] = __uint_as_float(u[j]) * sc;
-                        }
+                        row[f] = __uint_as_float(g[j]);
+                        if (!DUAL && two) row[f + GEMM_BM] = __uint_as_float(u[j]);
+                    }
+                }
+                // warp-uniform decision: the loads and shuffles below are warp-collective
+                if (DUAL && p.bad && __any_sync(0xffffffffu, probe != probe)) {
+                    // rare: recount this chunk's non-finite inputs exactly
+                    for (int j = 0; j < 32; ++j) {
+                        const float sc = __shfl_sync(0xffffffffu, my_sc, j);
+                        uint32_t gj, uj;
+                        tmem_ld_1(tl + c0 + j, gj);
+                        tmem_ld_1(tl + GEMM_BN + c0 + j, uj);
+                        tmem_ld_wait();
+                        if (c0 + j < np) count_bad(p.bad, __uint_as_float(gj) * sc, __uint_as_float(uj) * sc);
                     }
                 }
             }
             tc_fence_before_sync();
             mbar_arrive(&acc_empty);
+            GSTAT_END(1);
         }
+#ifdef ZMOE_GEMM_STATS
+        if (warp == GEMM_CWARPS + 2 && lane == 0) { GSTAT_STORE(0, 8); GSTAT_STORE(1, 9); }
+#endif
     }
     tc_fence_before_sync();
     __syncthreads();

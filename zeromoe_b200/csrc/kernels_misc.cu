@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const Rou
     if (s_ticket != n_tg - 1) return;
     __threadfence();
     PlanOut po{a.plan.hdr, a.plan.active, a.plan.offs, a.plan.slot, a.plan.item_offs_gu, a.plan.item_offs_dn,
-               a.plan.freq, a.plan.aoffs, a.plan.antok, a.nrt_gu, a.nrt_dn};
+               a.plan.freq, a.plan.aoffs, a.plan.antok, a.nrt_gu, a.nrt_dn, a.plan.pos};
     build_plan_cta(a.ids, a.T * a.K, a.E, po, cnt_s, pre_s, ids_s);
     if (tid == 0) a.ticket[0] = 0u;
 }
@@ -137,16 +137,21 @@ int launch_router_decode(const RouterArgs &a, cudaStream_t st) {
 // ------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) router_logits_gemm_kernel(const float *__restrict__ x,
                                                                  const float *__restrict__ wr,
-                                                                 float *__restrict__ logits, int T, int D, int E) {
+                                                                 float *__restrict__ logits, int T, int D, int E,
+                                                                 int ksplit) {
     __shared__ float xs[16][64 + 4], ws[16][64 + 4];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
     const int tid = threadIdx.x;
     const int t0 = blockIdx.y * 64, e0 = blockIdx.x * 64;
+    // blockIdx.z takes the z-th part of k and writes the z-th partial matrix (summed in a fixed order by
+    // router_select_kernel): more CTAs in flight than one 64 x 64 tile per SM gives
+    const int kper = D / ksplit, kbeg = blockIdx.z * kper, kend = kbeg + kper;
+    float *out = logits + (size_t)blockIdx.z * T * E;
     const int lr = tid >> 2, lc = (tid & 3) * 4;       // loader: row 0..63, k offset 0,4,8,12
     const int tm = (tid >> 4) * 4, tn = (tid & 15) * 4;  // compute: 4 tokens x 4 experts
     float acc[4][4] = {};
-    for (int k0 = 0; k0 < D; k0 += 16) {
+    for (int k0 = kbeg; k0 < kend; k0 += 16) {
         float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), wv = xv;
         if (t0 + lr < T) xv = *reinterpret_cast<const float4 *>(x + (size_t)(t0 + lr) * D + k0 + lc);
         if (e0 + lr < E) wv = *reinterpret_cast<const float4 *>(wr + (size_t)(e0 + lr) * D + k0 + lc);
@@ -169,31 +174,48 @@ __global__ void __launch_bounds__(256) router_logits_gemm_kernel(const float *__
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            if (t0 + tm + i < T && e0 + tn + j < E) logits[(size_t)(t0 + tm + i) * E + e0 + tn + j] = acc[i][j];
+            if (t0 + tm + i < T && e0 + tn + j < E) out[(size_t)(t0 + tm + i) * E + e0 + tn + j] = acc[i][j];
 }
 
-__global__ void __launch_bounds__(128) router_select_kernel(float *logits, const float *bias, int32_t *ids,
-                                                            float *weights, int T, RouterSpec sp) {
+// part != nullptr: the logits are the sum of `ksplit` partial matrices part[z][T, E], added in the order z = 0, 1, ...
+__global__ void __launch_bounds__(128) router_select_kernel(float *logits, const float *part, int ksplit,
+                                                            const float *bias, int32_t *ids, float *weights, int T,
+                                                            RouterSpec sp) {
     extern __shared__ float rsel[];
     pdl_wait_prior_grid();
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
     if (t >= T) return;
+    float *row = logits + (size_t)t * sp.E;
+    if (part) {
+        for (int e = lane; e < sp.E; e += 32) {
+            float v = part[(size_t)t * sp.E + e];
+            for (int z = 1; z < ksplit; ++z) v = __fadd_rn(v, part[((size_t)z * T + t) * sp.E + e]);
+            row[e] = v;
+        }
+        __syncwarp();
+    }
     float *prob_s = rsel + (size_t)warp * 2 * sp.E;
-    route_token_warp(sp, logits + (size_t)t * sp.E, logits + (size_t)t * sp.E, bias, ids + (size_t)t * sp.K,
-                     weights + (size_t)t * sp.K, prob_s, prob_s + sp.E, lane);
+    route_token_warp(sp, row, row, bias, ids + (size_t)t * sp.K, weights + (size_t)t * sp.K, prob_s, prob_s + sp.E, lane);
 }
 
 int launch_router_prefill(const RouterArgs &a, cudaStream_t st) {
     if (a.D % 16 || (size_t)8 * a.E * sizeof(float) > 48 * 1024) return ZMOE_ERR_SHAPE;
-    int rc = launch_pdl(router_logits_gemm_kernel, dim3((a.E + 63) / 64, (a.T + 63) / 64), dim3(256), 0, st, a.x, a.wr,
-                        a.logits, a.T, a.D, a.E) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+    // split k while the tiles alone leave most of the machine idle (a 64 x 64 tile per CTA, 8 warps)
+    const int tiles = ((a.E + 63) / 64) * ((a.T + 63) / 64);
+    int ksplit = 1;
+    if (a.logits_part && a.n_sm > 0)
+        while (ksplit < ROUTER_MAX_SPLIT && tiles * ksplit < 3 * a.n_sm && a.D % (32 * ksplit) == 0) ksplit *= 2;
+    float *dst = ksplit > 1 ? a.logits_part : a.logits;
+    int rc = launch_pdl(router_logits_gemm_kernel, dim3((a.E + 63) / 64, (a.T + 63) / 64, ksplit), dim3(256), 0, st, a.x,
+                        a.wr, dst, a.T, a.D, a.E, ksplit) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
     RouterSpec sp{a.E, a.K, a.gating, a.normalize, a.weight_scale, a.n_groups, a.n_groups_used};
     if (!rc)
         rc = launch_pdl(router_select_kernel, dim3((a.T + 3) / 4), dim3(128), (size_t)8 * a.E * sizeof(float), st,
-                        a.logits, a.bias, a.ids, a.weights, a.T, sp) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
-    if (!rc) rc = launch_quantize_rows(a.x, a.D, a.q8x, a.T, a.D, a.q8_layout, st);
+                        a.logits, (const float *)(ksplit > 1 ? a.logits_part : nullptr), ksplit, a.bias, a.ids, a.weights,
+                        a.T, sp) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+    if (!rc && a.want_q8x) rc = launch_quantize_rows(a.x, a.D, a.q8x, a.T, a.D, a.q8_layout, st);
     if (!rc) rc = launch_plan_from_ids(a.ids, a.T * a.K, a.E, a.plan, a.nrt_gu, a.nrt_dn, st);
     return rc;
 }
@@ -230,7 +252,7 @@ __global__ void __launch_bounds__(1024) plan_from_ids_kernel(const int32_t *ids,
 static int launch_plan(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
                        const RouteIngest &in, cudaStream_t st) {
     PlanOut po{plan.hdr, plan.active, plan.offs, plan.slot, plan.item_offs_gu, plan.item_offs_dn, plan.freq,
-               plan.aoffs, plan.antok, nrt_gu, nrt_dn};
+               plan.aoffs, plan.antok, nrt_gu, nrt_dn, plan.pos};
     const size_t smem = (size_t)2 * (E + 1) * sizeof(int) + (P <= ROUTER_IDS_SMEM ? (size_t)P * sizeof(int) : 0);
     if (smem > 48 * 1024) return ZMOE_ERR_SHAPE;
     return launch_pdl(plan_from_ids_kernel, dim3(1), dim3(1024), smem, st, ids, P, E, po, in) == cudaSuccess

@@ -113,6 +113,26 @@ __device__ __forceinline__ float swiglu_f(float g, float u, float clamp, int fus
     return out;
 }
 
+// The same function for the tensor-core path's epilogue, where one warp per scheduler works through a whole
+// accumulator tile while the tensor memory is held: the quotient comes from the reciprocal unit
+// (__fdividef, at most 2 ulp from the correctly rounded one) so that no slow-path branch breaks up the
+// interleaving of the columns' dependency chains.  The path's results are within 3e-4 of the CPU path anyway.
+__device__ __forceinline__ float swiglu_fast(float g, float u, float clamp, int fused) {
+    float out;
+    if (fused) {
+        if (clamp > 0.0f) {
+            g = fminf(g, clamp);
+            u = fmaxf(-clamp, fminf(clamp, u));
+        }
+        out = __fdividef(g, 1.0f + expf(-g)) * u;
+    } else {
+        g = __fdividef(g, 1.0f + expf(-g));
+        out = g * u;
+        if (clamp > 0.0f) out = fmaxf(-clamp, fminf(clamp, out));
+    }
+    return out;
+}
+
 // Non-finite inputs of the fused SwiGLU, counted as reference kernels/math/expert_activation.cu:42-44
 // does (bad[0]: one of the two is NaN; bad[1]: none is NaN, one is infinite).  The test is one
 // instruction on the common path; the atomics run only when something is wrong.

@@ -35,6 +35,7 @@ struct PlanOut {
     int *aoffs;        // [E] offs[active[a]]
     int *antok;        // [E] pairs of active[a]
     int nrt_gu, nrt_dn;  // row tiles per expert of the two projections
+    int *pos = nullptr;  // [P] inverse of slot: position of pair p in expert order, -1 for an inactive route; may be null
 };
 
 __device__ __forceinline__ float gate_scalar(float x, int gating) {
@@ -236,14 +237,19 @@ __device__ void build_plan_cta(const int32_t *ids, int P, int E, const PlanOut &
                     pre_s[e] = base + __popc(peers);
                 }
                 base = __shfl_sync(0xffffffffu, base, leader);
-                if (on) po.slot[base + __popc(peers & ((1u << lane) - 1u))] = p;
+                const int at = base + __popc(peers & ((1u << lane) - 1u));
+                if (on) po.slot[at] = p;
+                if (po.pos && p < P) po.pos[p] = on ? at : -1;
                 __syncwarp();
             }
         }
     } else {
         for (int p = tid; p < P; p += nt) {
             const int e = ids[p];
-            if (e >= 0 && e < E) po.slot[atomicAdd(&pre_s[e], 1)] = p;
+            const bool on = e >= 0 && e < E;
+            const int at = on ? atomicAdd(&pre_s[e], 1) : -1;
+            if (on) po.slot[at] = p;
+            if (po.pos) po.pos[p] = at;
         }
     }
 }

@@ -78,6 +78,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is
+// incomplete: a waiting warp then takes no issue slots from the warps that do the work
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait built on it: at most `limit` suspensions of up to `ns` nanoseconds each
+__device__ __forceinline__ bool mbar_wait_suspend(uint64_t *bar, uint32_t parity, uint32_t ns = 2000,
+                                                  uint32_t limit = (1u << 16)) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait_suspend(bar, parity, ns)) return true;
+    return false;
+}
 // Bounded wait: gives up after `limit` polls and reports failure instead of
 // spinning forever; callers raise an error flag and unwind.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 19)) {

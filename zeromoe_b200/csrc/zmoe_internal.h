@@ -30,6 +30,7 @@ struct PlanBuffers {
     int *hdr = nullptr, *active = nullptr, *offs = nullptr, *slot = nullptr;
     int *item_offs_gu = nullptr, *item_offs_dn = nullptr, *freq = nullptr;
     int *aoffs = nullptr, *antok = nullptr;
+    int *pos = nullptr;    // [P] position of each pair in expert order (inverse of slot), -1 = inactive; optional
     int cap_e = 0;
 };
 
@@ -51,7 +52,11 @@ struct RouterArgs {
     PlanBuffers plan;
     int nrt_gu, nrt_dn;
     unsigned *ticket;      // 1 + ROUTER_MAX_GROUPS zero-initialised counters, left at zero
+    bool want_q8x = true;  // large batches: also quantise x into q8x (the tensor-core path does not read it)
+    float *logits_part = nullptr;  // large batches: [ROUTER_MAX_SPLIT][T, E] partial logits of a k-split router GEMM, or null
+    int n_sm = 0;
 };
+constexpr int ROUTER_MAX_SPLIT = 4;
 
 // geometry of one mmid launch, fixed per (type, I, O)
 struct MmidGeom {
@@ -110,9 +115,15 @@ struct GemmLaunch {
     int n_sm;
 };
 bool gemm_sm100_supported(int type, int I, int O);
+unsigned long long *gemm_stats_buffer(int which);
+int gemm_stats_read(unsigned long long *out32);
 int launch_gemm_sm100(const GemmLaunch &L, cudaStream_t st);
 int launch_q8_roundtrip_f16(const float *x, int ldx, void *out_f16, float *scale, const PlanBuffers &plan,
                             int max_rows, int xdiv, int I, cudaStream_t st);
+// the same for the layer input, where the K pairs of a token share one source row: the row is passed through
+// Q8_K once and written to the K positions plan.pos names (needs plan.pos)
+int launch_q8_roundtrip_tokens_f16(const float *x, int ldx, void *out_f16, float *scale, const PlanBuffers &plan,
+                                   int T, int K, int I, cudaStream_t st);
 
 int launch_router_decode(const RouterArgs &a, cudaStream_t st);
 int launch_router_prefill(const RouterArgs &a, cudaStream_t st);  // four launches; for large T

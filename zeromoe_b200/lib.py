@@ -26,6 +26,7 @@ EXPORTS = [
     "zmoe_get_expert_freq", "zmoe_copy_routes", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_set_path", "zmoe_ctx_check", "zmoe_kernel_launches",
     "zmoe_quantize_q8_K", "zmoe_block_isums",
     "zmoe_device_status", "zmoe_selftest_wait_expiry", "zmoe_ctx_bad_counts", "zmoe_gemm_min_pairs_per_expert",
+    "zmoe_debug_gemm_cycles",
 ]
 
 
@@ -112,6 +113,7 @@ def load():
     L.zmoe_block_isums.argtypes = [i, vp, vp, vp, vp, i, i, vp]
     L.zmoe_selftest_wait_expiry.argtypes = [vp]
     L.zmoe_ctx_bad_counts.argtypes = [vp, vp, i]
+    L.zmoe_debug_gemm_cycles.argtypes = [vp]
     _lib = L
     return L
 
