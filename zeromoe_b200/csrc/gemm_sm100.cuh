@@ -17,10 +17,14 @@
 //   warps 0-15 converters: read the raw blocks from shared memory and write them as fp16 in the
 //              128-byte-swizzled K-major layout tcgen05 reads, 64 k per pipeline stage; one of
 //              them issues the tiled copy of the matching 64-k slice of the activation rows,
-//              which were gathered into expert order beforehand.
+//              which were gathered into expert order beforehand.  The same warps drain the
+//              accumulators of a finished tile (tcgen05.ld, SwiGLU in DUAL mode, f32 stores): both
+//              accumulators fill the tensor memory, so the next tile's MMAs wait for the drain, and
+//              sixteen warps (four per quarter of the tensor-memory lanes, two 32-column chunks each)
+//              finish it in a quarter of the time four dedicated warps need.  The drain of tile t runs
+//              after the first stage of tile t+1 has been converted, when tile t's last MMAs are done.
 //   warp 16    issues tcgen05.mma (M = 128 weight rows, N = pairs, K = 16 per instruction) for
 //              both halves, accumulators in tensor memory; tcgen05.commit releases the stage.
-//   warps 18-21 epilogue: tcgen05.ld the accumulators, apply SwiGLU in DUAL mode, store f32.
 // Activations arrive already rounded through Q8_K (value = d * q) as fp16, each row divided by a
 // power of two that brings its largest value near 2^13 (undone exactly in the epilogue), so the
 // result follows the reference CPU path's activation quantisation and cannot overflow fp16;
@@ -43,7 +47,7 @@ constexpr int GEMM_NSTAGE = 2;      // fp16 operand stages
 constexpr int GEMM_NRAW = 2;        // raw super-block slots
 constexpr int GEMM_CWARPS = 16;     // converter warps
 constexpr int GEMM_CONVERTERS = 32 * GEMM_CWARPS;
-constexpr int GEMM_THREADS = GEMM_CONVERTERS + 32 + 32 + 128;
+constexpr int GEMM_THREADS = GEMM_CONVERTERS + 32 + 32;
 constexpr int GEMM_MAX_ACTIVE = 512;
 
 // bytes between the raw copies of consecutive rows in shared memory: room for one super-block plus its
@@ -142,7 +146,7 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
             mbar_init(&raw_empty[s], GEMM_CWARPS);
         }
         mbar_init(&acc_full, 1);
-        mbar_init(&acc_empty, 128);
+        mbar_init(&acc_empty, GEMM_CWARPS);
         mbar_init_fence();
     }
     if (warp == GEMM_CWARPS) tmem_alloc(&tmem_slot, TMEM_COLS);
@@ -206,13 +210,106 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) st_off[c] = which * A_BYTES + swz128_offset(r, 32 * half + 8 * c);
         GSTAT_DECL;
-        for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+        // ---- drain of a finished tile's accumulators (all converter warps) ----
+        // warp w reads its quarter q = w % 4 of the tensor-memory lanes (rows) and the 32-column chunks
+        // w / 4 and w / 4 + 4 of the tile's pairs; lane j of a chunk's metadata holds column 32 c + j
+        const int q = warp & 3, cset = warp >> 2;
+        const uint32_t tl = tmem_base + ((uint32_t)(32 * q) << 16);
+        int nt = 0;                      // tiles converted so far
+        int d_m0 = 0, d_np = 0;          // the tile waiting for its drain
+        bool d_two = false;
+        int d_pair[2] = {-1, -1};
+        float d_sc[2] = {0.f, 0.f};
+        auto drain = [&]() -> bool {
+#ifdef ZMOE_GEMM_STATS
+            unsigned long long e_t0 = 0;
+            if (gs_on) e_t0 = clock64();
+#endif
+            if (!mbar_wait_suspend(&acc_full, (nt - 1) & 1)) return false;
+            tc_fence_after_sync();
+#ifdef ZMOE_GEMM_STATS
+            if (gs_on && tid == 32) { const unsigned long long t1 = clock64(); p.stats[8] += t1 - e_t0; e_t0 = t1; }
+#endif
+            const int f = d_m0 + 32 * q + lane;   // this thread's weight row (first half)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int c0 = 32 * (cset + 4 * i);
+                if (c0 >= d_np) break;
+                uint32_t g[32], u[32];
+                tmem_ld_32x32(tl + c0, g);
+                if (d_two) tmem_ld_32x32(tl + GEMM_BN + c0, u);
+                const int my_pair = d_pair[i];
+                const float my_sc = d_sc[i];
+                tmem_ld_wait();
+                // the arithmetic of all 32 columns first, without branches, so that the columns' dependency
+                // chains interleave; x - x is 0 for a finite x and NaN otherwise: the sum flags a non-finite
+                // gate / up value
+                float probe = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float sc = __shfl_sync(0xffffffffu, my_sc, j);
+                    const float gv = __uint_as_float(g[j]) * sc;
+                    if (DUAL) {
+                        const float uv = __uint_as_float(u[j]) * sc;
+                        probe += (gv - gv) + (uv - uv);
+                        g[j] = __float_as_uint(swiglu_fast(gv, uv, p.clamp, p.clamp_fused));
+                    } else {
+                        g[j] = __float_as_uint(gv);
+                        if (d_two) u[j] = __float_as_uint(__uint_as_float(u[j]) * sc);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int pair = __shfl_sync(0xffffffffu, my_pair, j);
+                    if (pair >= 0) {
+                        float *row = p.y + (size_t)pair * p.ldy;
+                        row[f] = __uint_as_float(g[j]);
+                        if (!DUAL && d_two) row[f + GEMM_BM] = __uint_as_float(u[j]);
+                    }
+                }
+                // warp-uniform decision: the loads and shuffles below are warp-collective
+                if (DUAL && p.bad && __any_sync(0xffffffffu, probe != probe)) {
+                    // rare: recount this chunk's non-finite inputs exactly
+                    for (int j = 0; j < 32; ++j) {
+                        const float sc = __shfl_sync(0xffffffffu, my_sc, j);
+                        uint32_t gj, uj;
+                        tmem_ld_1(tl + c0 + j, gj);
+                        tmem_ld_1(tl + GEMM_BN + c0 + j, uj);
+                        tmem_ld_wait();
+                        if (c0 + j < d_np) count_bad(p.bad, __uint_as_float(gj) * sc, __uint_as_float(uj) * sc);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty);
+#ifdef ZMOE_GEMM_STATS
+            if (gs_on && tid == 32) p.stats[9] += clock64() - e_t0;
+#endif
+            return true;
+        };
+        for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++nt) {
             int e, m0, p0, np;
             tile_info(tile, e, m0, p0, np);
             const int ncols = (np + 15) & ~15;
             const bool worker = which == 0 || has_half1(m0);
+            // pair ids and scales of this warp's two column chunks: fetched now, used by the drain much later
+            int n_pair[2];
+            float n_sc[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int col = 32 * (cset + 4 * i) + lane;
+                n_pair[i] = col < np ? p.slot[p0 + col] : -1;
+                n_sc[i] = col < np ? p.xscale[p0 + col] : 0.f;
+            }
             uint32_t blk = 0;
             for (int ks = 0; ks < ksteps; ++ks, ++it) {
+                // the previous tile's accumulators: its last MMAs finish while this tile's first stage is converted
+                if (ks == 1 && nt > 0 && !drain()) {
+                    atomicExch(p.err, 6);
+                    alive = false;
+                    break;
+                }
                 const int s = it % GEMM_NSTAGE;
                 const int rs = rc % GEMM_NRAW;
                 GSTAT_BEGIN();
@@ -263,7 +360,11 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
                 if ((ks & 3) == 3) ++rc;
                 GSTAT_END(3);
             }
+            d_m0 = m0; d_np = np; d_two = has_half1(m0);
+            d_pair[0] = n_pair[0]; d_pair[1] = n_pair[1];
+            d_sc[0] = n_sc[0]; d_sc[1] = n_sc[1];
         }
+        if (alive && nt > 0 && !drain()) atomicExch(p.err, 6);
 #ifdef ZMOE_GEMM_STATS
         if (tid == 32) {
             if (gs_on) p.stats[0] += (unsigned long long)it;
@@ -358,90 +459,6 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
         }
 #ifdef ZMOE_GEMM_STATS
         if (lane == 0) { GSTAT_STORE(0, 10); GSTAT_STORE(1, 11); }
-#endif
-    } else {
-        // ------------------------------- epilogue --------------------------------------
-        const int q = warp & 3;              // the warp's quarter of the 128 tensor-memory lanes
-        int nt = 0;
-        GSTAT_DECL;
-        for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++nt) {
-            int e, m0, p0, np;
-            tile_info(tile, e, m0, p0, np);
-            const bool two = has_half1(m0);
-            // pair ids and scales of the tile's columns, lane j of chunk c holding column 32 c + j: fetched now,
-            // while the tile's MMAs are still running
-            int mp[GEMM_BN / 32];
-            float ms[GEMM_BN / 32];
-#pragma unroll
-            for (int c = 0; c < GEMM_BN / 32; ++c) {
-                const int col = 32 * c + lane;
-                mp[c] = col < np ? p.slot[p0 + col] : -1;
-                ms[c] = col < np ? p.xscale[p0 + col] : 0.f;
-            }
-            GSTAT_BEGIN();
-            if (!mbar_wait_suspend(&acc_full, nt & 1)) {
-                if (lane == 0) atomicExch(p.err, 6);
-                alive = false;
-                break;
-            }
-            GSTAT_END(0);
-            tc_fence_after_sync();
-            const int f = m0 + 32 * q + lane;   // this thread's weight row (first half)
-            const uint32_t tl = tmem_base + ((uint32_t)(32 * q) << 16);
-            for (int c0 = 0; c0 < np; c0 += 32) {
-                uint32_t g[32], u[32];
-                tmem_ld_32x32(tl + c0, g);
-                if (two) tmem_ld_32x32(tl + GEMM_BN + c0, u);
-                // column metadata (fetched before the wait for the accumulators): lane j holds pair id and
-                // scale of column c0 + j, the loops below broadcast them
-                const int my_pair = mp[c0 >> 5];
-                const float my_sc = ms[c0 >> 5];
-                tmem_ld_wait();
-                // the arithmetic of all 32 columns first, without branches, so that the columns' dependency
-                // chains interleave (one warp per scheduler does this while the tensor memory is held);
-                // x - x is 0 for a finite x and NaN otherwise: the sum flags a non-finite gate / up value
-                float probe = 0.f;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float sc = __shfl_sync(0xffffffffu, my_sc, j);
-                    const float gv = __uint_as_float(g[j]) * sc;
-                    if (DUAL) {
-                        const float uv = __uint_as_float(u[j]) * sc;
-                        probe += (gv - gv) + (uv - uv);
-                        g[j] = __float_as_uint(swiglu_fast(gv, uv, p.clamp, p.clamp_fused));
-                    } else {
-                        g[j] = __float_as_uint(gv);
-                        if (two) u[j] = __float_as_uint(__uint_as_float(u[j]) * sc);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int pair = __shfl_sync(0xffffffffu, my_pair, j);
-                    if (pair >= 0) {
-                        float *row = p.y + (size_t)pair * p.ldy;
-                        row[f] = __uint_as_float(g[j]);
-                        if (!DUAL && two) row[f + GEMM_BM] = __uint_as_float(u[j]);
-                    }
-                }
-                // warp-uniform decision: the loads and shuffles below are warp-collective
-                if (DUAL && p.bad && __any_sync(0xffffffffu, probe != probe)) {
-                    // rare: recount this chunk's non-finite inputs exactly
-                    for (int j = 0; j < 32; ++j) {
-                        const float sc = __shfl_sync(0xffffffffu, my_sc, j);
-                        uint32_t gj, uj;
-                        tmem_ld_1(tl + c0 + j, gj);
-                        tmem_ld_1(tl + GEMM_BN + c0 + j, uj);
-                        tmem_ld_wait();
-                        if (c0 + j < np) count_bad(p.bad, __uint_as_float(gj) * sc, __uint_as_float(uj) * sc);
-                    }
-                }
-            }
-            tc_fence_before_sync();
-            mbar_arrive(&acc_empty);
-            GSTAT_END(1);
-        }
-#ifdef ZMOE_GEMM_STATS
-        if (warp == GEMM_CWARPS + 2 && lane == 0) { GSTAT_STORE(0, 8); GSTAT_STORE(1, 9); }
 #endif
     }
     tc_fence_before_sync();
