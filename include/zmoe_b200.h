@@ -44,6 +44,7 @@ extern "C" {
 #define ZMOE_ERR_CAPACITY (-6)    /* more tokens than the context was created for */
 #define ZMOE_ERR_DEVICE_WAIT (-7) /* a bounded device-side wait expired */
 #define ZMOE_ERR_STATE (-8)       /* wrong call order */
+#define ZMOE_ERR_COMM (-9)        /* NCCL is missing or one of its calls failed */
 
 /* GGUF quantisation type ids (reference models/base/gguf_loader.hpp:28-51) */
 #define ZMOE_TYPE_Q2_K 10
@@ -253,7 +254,46 @@ int zmoe_debug_gemm_cycles(uint64_t *counters32_host);
 uint64_t zmoe_kernel_launches(void);
 
 /* =========================================================================
- * 4. Parity hooks -- expose the integer stages so tests can compare them
+ * 4. Expert parallelism over the GPUs of one node -- no counterpart in the reference (it has no
+ *    collectives; its multi-GPU support is placement plus cudaMemcpyPeer, core/gpu_topology.cpp:1644).
+ *    Rank r of N holds the experts [r * E / N, (r + 1) * E / N) of a layer in a zmoe_layer of its own and
+ *    brings its own tokens.  Per layer, token rows travel once to every rank that owns one of their
+ *    experts (all-to-all by per-destination counts, grouped ncclSend / ncclRecv), each rank runs its experts
+ *    over what it received with routes of experts held elsewhere inactive -- the ownership convention of
+ *    the reference's hot / cold split (backends/ggml/moe_partial_route_ggml.hpp:13-58) -- and one
+ *    pre-weighted, pre-reduced row per (token, rank) travels back and is added in ascending rank order.
+ *    Remote rows always land in local memory through NCCL before a kernel reads them.  NCCL is loaded with
+ *    dlopen at first use: without it these calls return ZMOE_ERR_COMM and the rest of the library works.
+ * ========================================================================= */
+typedef struct zmoe_ep zmoe_ep;
+
+/* thin wrappers for hosts that do not create NCCL communicators themselves: id128 is a 128-byte
+ * ncclUniqueId made on one rank and handed to all; comm_init runs ncclCommInitRank on the current device */
+int zmoe_ep_unique_id(void *id128);
+int zmoe_ep_comm_init(const void *id128, int rank, int world, void **comm_out);
+int zmoe_ep_comm_destroy(void *comm);
+
+/* nccl_comm: an ncclComm_t (as void*) with one rank per GPU, borrowed.  max_tokens: tokens a rank brings per
+ * call; max_recv_tokens: rows it may receive (at most world * max_tokens; the local layer's context must be
+ * created for that many tokens).  Allocates the exchange buffers. */
+int zmoe_ep_create(void *nccl_comm, int rank, int world, int max_tokens, int max_recv_tokens, int d_model, int topk,
+                   zmoe_ep **out);
+void zmoe_ep_destroy(zmoe_ep *ep);
+/* One expert-parallel MoE layer.  router: a layer over ALL experts of the model with the router tensors set
+ * (only zmoe_route is run on it); local: the layer holding this rank's experts; shared: the shared expert
+ * (zmoe_dense_ffn layer) added on the tokens' home rank, or NULL.  x_dev, out_dev: [T, d_model].
+ * Synchronises `stream` once per call (the transfer sizes go through the host); every rank of the
+ * communicator must make the call. */
+int zmoe_ep_forward(zmoe_ep *ep, zmoe_layer *router, zmoe_layer *local, zmoe_layer *shared, const float *x_dev,
+                    float *out_dev, int T, void *stream);
+/* the same with routes supplied: ids are the model's expert numbers (n_experts_total of them) */
+int zmoe_ep_forward_routed(zmoe_ep *ep, zmoe_layer *local, zmoe_layer *shared, int n_experts_total, const float *x_dev,
+                           const int32_t *ids_dev, const float *weights_dev, float *out_dev, int T, void *stream);
+/* token rows this rank sent and received in its last exchange */
+int zmoe_ep_last_rows(zmoe_ep *ep, int64_t *sent_rows, int64_t *recv_rows);
+
+/* =========================================================================
+ * 5. Parity hooks -- expose the integer stages so tests can compare them
  *    bit-for-bit with the CPU path.
  * ========================================================================= */
 /* x_dev [rows, I] f32 -> blocks_dev: rows * I/256 ggml Q8_K blocks of 292 bytes

@@ -30,6 +30,62 @@ def _inputs():
     return wg, wu, wd, xs, ids, ws
 
 
+def _worker_a2a(rank, world, port, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, ROOT)
+    from oracle import oracle as O
+    from zeromoe_b200 import expert_parallel as ep
+    wg, wu, wd, xs, ids, ws = _inputs()
+    e_lo, e_hi = ep.expert_range(rank, world, E)
+    L = O.make_layer(D, F, e_hi - e_lo, K, TYPES, wg[e_lo:e_hi].copy(), wu[e_lo:e_hi].copy(), wd[e_lo:e_hi].copy())
+    seen = {}
+
+    def compute(x_recv, ids_recv, w_recv):
+        seen["rows"] = x_recv.shape[0]
+        local = ep.localise_ids(ids_recv, e_lo, e_hi)
+        assert bool((local >= 0).any(dim=1).all()), "a row arrived that names no local expert"
+        return torch.from_numpy(O.moe_ffn(L, x_recv.numpy(), local.numpy(), w_recv.numpy()))
+    my_ids = ids[rank].copy()
+    if rank == 1:
+        my_ids[2, :] = -1            # a token with no active route: goes nowhere, output row is zero
+    out = ep.exchange_forward_a2a(torch.from_numpy(xs[rank]), torch.from_numpy(my_ids), torch.from_numpy(ws[rank]), E,
+                                  compute)
+    results[rank] = (out.numpy(), seen.get("rows", 0))
+    dist.destroy_process_group()
+
+
+def test_two_rank_all_to_all_matches_single_rank(oracle):
+    """token rows travel once to every rank that owns one of their experts and come back pre-reduced"""
+    world = 2
+    port = 31000 + os.getpid() % 2000
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker_a2a, args=(world, port, results), nprocs=world, join=True)
+    wg, wu, wd, xs, ids, ws = _inputs()
+    L = oracle.make_layer(D, F, E, K, TYPES, wg, wu, wd)
+    ids[1][2, :] = -1
+    total_rows = 0
+    for r in range(world):
+        ref = oracle.moe_ffn(L, xs[r], ids[r], ws[r])
+        got, rows = results[r]
+        total_rows += rows
+        assert np.abs(got - ref).max() / np.linalg.norm(ref) < 1e-6
+    assert np.all(results[1][0][2] == 0.0)
+    # every (token, owning rank) pair is one row: no more than tokens x ranks, no fewer than routed tokens
+    assert 2 * T - 1 <= total_rows <= 2 * world * T
+
+
+def test_destination_plan_is_stable():
+    from zeromoe_b200 import expert_parallel as ep
+    ids = torch.tensor([[0, 5], [6, 7], [-1, 9], [3, 1]], dtype=torch.int32)
+    mask, counts, tokens = ep.destination_plan(ids, 8, 2)       # ranks own experts 0..3 and 4..7; 9 is out of range
+    assert mask.tolist() == [[True, True], [False, True], [False, False], [True, False]]
+    assert counts == [2, 2]
+    assert [t.tolist() for t in tokens] == [[0, 3], [0, 1]]
+
+
 def _worker(rank, world, port, results, own_mapping=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)

@@ -143,6 +143,19 @@ struct zmoe_layer {
     int nrt_gu, nrt_dn;
 };
 
+namespace zmoe {
+int layer_route_table(zmoe_layer *L, const int32_t **ids_dev, const float **weights_dev, int *n_experts) {
+    if (!L || !ids_dev || !weights_dev || !n_experts) return ZMOE_ERR_ARG;
+    if (L->ctx->routed_t <= 0) return ZMOE_ERR_STATE;
+    *ids_dev = L->ctx->ids;
+    *weights_dev = L->ctx->weights;
+    *n_experts = L->d.n_experts;
+    return ZMOE_OK;
+}
+zmoe_ctx *layer_context(zmoe_layer *L) { return L ? L->ctx : nullptr; }
+int context_path(const zmoe_ctx *c) { return c ? c->path : 0; }
+}  // namespace zmoe
+
 extern "C" {
 
 int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_experts, int max_topk, zmoe_ctx **out) {

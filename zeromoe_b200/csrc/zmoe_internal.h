@@ -25,6 +25,12 @@ int raise_dynamic_smem(const void *fn, size_t bytes);
 // point has not run on this device (implemented in noalloc.cu)
 int noalloc_take_error(int *out);
 
+// accessors of the opaque handles for the other .cu files (implemented in api.cu)
+// device pointers of the route table a layer's context currently holds, and the layer's expert count
+int layer_route_table(zmoe_layer *layer, const int32_t **ids_dev, const float **weights_dev, int *n_experts);
+zmoe_ctx *layer_context(zmoe_layer *layer);
+int context_path(const zmoe_ctx *ctx);
+
 // device-resident routing plan buffers
 struct PlanBuffers {
     int *hdr = nullptr, *active = nullptr, *offs = nullptr, *slot = nullptr;

@@ -13,7 +13,7 @@ BLOCK_BYTES = {Q2_K: 84, Q3_K: 110, Q4_K: 144, IQ2_XXS: 66}
 GGML_F32, GGML_I32 = 0, 26
 
 ERRORS = {0: "OK", -1: "ARG", -2: "TYPE", -3: "SHAPE", -4: "ALIGN", -5: "CUDA", -6: "CAPACITY",
-          -7: "DEVICE_WAIT", -8: "STATE"}
+          -7: "DEVICE_WAIT", -8: "STATE", -9: "COMM"}
 
 # every symbol include/zmoe_b200.h declares
 EXPORTS = [
@@ -27,6 +27,8 @@ EXPORTS = [
     "zmoe_quantize_q8_K", "zmoe_block_isums",
     "zmoe_device_status", "zmoe_selftest_wait_expiry", "zmoe_ctx_bad_counts", "zmoe_gemm_min_pairs_per_expert",
     "zmoe_debug_gemm_cycles",
+    "zmoe_ep_unique_id", "zmoe_ep_comm_init", "zmoe_ep_comm_destroy", "zmoe_ep_create", "zmoe_ep_destroy",
+    "zmoe_ep_forward", "zmoe_ep_forward_routed", "zmoe_ep_last_rows",
 ]
 
 
@@ -114,6 +116,15 @@ def load():
     L.zmoe_selftest_wait_expiry.argtypes = [vp]
     L.zmoe_ctx_bad_counts.argtypes = [vp, vp, i]
     L.zmoe_debug_gemm_cycles.argtypes = [vp]
+    L.zmoe_ep_unique_id.argtypes = [vp]
+    L.zmoe_ep_comm_init.argtypes = [vp, i, i, C.POINTER(vp)]
+    L.zmoe_ep_comm_destroy.argtypes = [vp]
+    L.zmoe_ep_create.argtypes = [vp, i, i, i, i, i, i, C.POINTER(vp)]
+    L.zmoe_ep_destroy.argtypes = [vp]
+    L.zmoe_ep_destroy.restype = None
+    L.zmoe_ep_forward.argtypes = [vp, vp, vp, vp, vp, vp, i, vp]
+    L.zmoe_ep_forward_routed.argtypes = [vp, vp, vp, i, vp, vp, vp, vp, i, vp]
+    L.zmoe_ep_last_rows.argtypes = [vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
     _lib = L
     return L
 
