@@ -76,6 +76,13 @@ void launch_q3_K_matmul_stream(float *y, const float *x, const void *w, int S, i
 void launch_q4_K_matmul(float *y, const float *x, const void *w, int S, int I, int O);
 /* replaces reference kernels/quant/iq2_matmul.cu:180-183 */
 void launch_iq2_xxs_matmul(float *y, const float *x, const void *w, int S, int I, int O);
+/* replaces reference kernels/quant/q8_0_matmul.cu:189-221: W packed rows of 34-byte Q8_0 blocks
+ * {fp16 d; int8 q[32]}, I a multiple of 32.  The activation rows are quantised to Q8_0 as well
+ * and blocks are multiplied in integers, as the reference's CPU path (ggml MUL_MAT) does. */
+void launch_q8_0_matmul(float *y, const float *x, const void *weights, int S, int I, int O);
+void launch_q8_0_matmul_stream(float *y, const float *x, const void *weights, int S, int I, int O, void *stream);
+/* replaces reference kernels/math/rmsnorm.cu:80-83: y[S, D] = x * rsqrt(mean(x^2) + eps) * w, D a multiple of 4 */
+void launch_rmsnorm(float *y, const float *x, const float *w, int S, int D, float eps);
 
 /* replaces reference kernels/math/expert_activation.cu:61-70 */
 void launch_expert_swiglu(float *prod, const float *gate, const float *up, int n, float clamp, int fused,
@@ -293,7 +300,44 @@ int zmoe_ep_forward_routed(zmoe_ep *ep, zmoe_layer *local, zmoe_layer *shared, i
 int zmoe_ep_last_rows(zmoe_ep *ep, int64_t *sent_rows, int64_t *recv_rows);
 
 /* =========================================================================
- * 5. Parity hooks -- expose the integer stages so tests can compare them
+ * 5. Decoder step around the MoE block -- the fifth benchmark configuration end to end on the device: token
+ *    embedding, per layer RMSNorm -> Q8_0 q/k/v projection -> RoPE (interleaved pairs, reference
+ *    models/base/rope.hpp:52-118 without YaRN) -> grouped-query attention over an f16 KV cache (scores
+ *    q.k / sqrt(head_dim), reference core/attention_layer.cpp:2633-2690) -> Q8_0 output projection added to the
+ *    residual -> RMSNorm -> MoE block (sections 3) added to the residual; then RMSNorm, Q8_0 output head and
+ *    greedy arg-max on the last token.  One sequence; the position and the sampled token stay on the
+ *    device, so steps of one token can be enqueued back to back (or captured once and replayed) without a
+ *    host round trip.  All tensors are borrowed device pointers.
+ * ========================================================================= */
+typedef struct zmoe_decoder zmoe_decoder;
+typedef struct zmoe_decoder_desc {
+    int n_layers, d_model, n_heads, n_kv_heads, head_dim; /* head_dim 64 or 128 */
+    int vocab, max_ctx, max_tokens;                       /* KV cache positions; tokens per step */
+    float rms_eps, rope_theta;
+    /* arrays of n_layers device pointers */
+    const float *const *attn_norm_w; /* [d_model] */
+    const void *const *wqkv;         /* Q8_0 [(n_heads + 2 n_kv_heads) * head_dim rows of d_model]: q, k, v rows in this order */
+    const void *const *wo;           /* Q8_0 [d_model rows of n_heads * head_dim] */
+    const float *const *ffn_norm_w;  /* [d_model] */
+    zmoe_layer *const *moe;          /* the layers' MoE blocks, created on a context of at least max_tokens tokens */
+    const void *tok_embd;            /* Q8_0 [vocab rows of d_model] */
+    const float *out_norm_w;         /* [d_model] */
+    const void *lm_head;             /* Q8_0 [vocab rows of d_model] */
+} zmoe_decoder_desc;
+int zmoe_decoder_create(const zmoe_decoder_desc *desc, zmoe_decoder **out);
+void zmoe_decoder_destroy(zmoe_decoder *dec);
+/* position back to 0 (the cache is overwritten as positions are reused) */
+int zmoe_decoder_reset(zmoe_decoder *dec, void *stream);
+/* T tokens at positions pos .. pos + T - 1 (T > 1: prompt processing, causal); tokens_dev == NULL with T == 1
+ * takes the token the previous step sampled.  Leaves the arg-max of the last token's logits as the next
+ * token and advances the position by T. */
+int zmoe_decoder_step(zmoe_decoder *dec, const int32_t *tokens_dev, int T, void *stream);
+/* synchronous reads of the sampled token, the position and the first n_logits logits of the last step (NULL
+ * to skip); synchronise the stream first */
+int zmoe_decoder_read(zmoe_decoder *dec, int32_t *next_token_host, int32_t *pos_host, float *logits_host, int n_logits);
+
+/* =========================================================================
+ * 6. Parity hooks -- expose the integer stages so tests can compare them
  *    bit-for-bit with the CPU path.
  * ========================================================================= */
 /* x_dev [rows, I] f32 -> blocks_dev: rows * I/256 ggml Q8_K blocks of 292 bytes

@@ -20,8 +20,10 @@ Q8K_BYTES = 292
 
 def build(force=False):
     """Compile the oracle (and the reference shim when the reference checkout exists)."""
-    if force or not os.path.exists(LIB_PATH):
-        subprocess.check_call(["make", "-C", HERE, "-s", "libzmoe_oracle.so"])
+    srcs = [os.path.join(HERE, f) for f in ("zmoe_oracle.c", "zmoe_oracle_fast.c", "zmoe_oracle_dense.c", "zmoe_oracle.h")]
+    stale = os.path.exists(LIB_PATH) and any(os.path.getmtime(f) > os.path.getmtime(LIB_PATH) for f in srcs)
+    if force or stale or not os.path.exists(LIB_PATH):
+        subprocess.check_call(["make", "-C", HERE, "-s", "-B", "libzmoe_oracle.so"])
     # the reference checkout, where there is one: named by ZMOE_REFERENCE_ROOT, else looked for beside
     # this repository (../reference); without it the `ref` target is skipped
     ref_root = os.environ.get("ZMOE_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
@@ -148,6 +150,39 @@ def mul_mat_id(qtype, x, w, expert_stride, ids, T, K, E, I, O, x_per_route):
     y = np.zeros((T, K, O), dtype=np.float32)
     lib().zo_mul_mat_id(C.c_int(qtype), _p(y), _p(x), _p(w), C.c_size_t(expert_stride), _p(ids),
                         C.c_int(T), C.c_int(K), C.c_int(E), C.c_int(I), C.c_int(O), C.c_int(x_per_route))
+    return y
+
+
+Q8_0 = 8
+Q8_0_BYTES = 34
+
+
+def quantize_q8_0(x):
+    """x [..., k] f32 -> uint8 [..., k/32*34] (ggml Q8_0 blocks)"""
+    x = _f32(x)
+    k = x.shape[-1]
+    rows = x.reshape(-1, k)
+    out = np.zeros((rows.shape[0], k // 32 * Q8_0_BYTES), dtype=np.uint8)
+    for r in range(rows.shape[0]):
+        lib().zo_quantize_row_q8_0(_p(rows[r]), _p(out[r]), C.c_int64(k))
+    return out.reshape(x.shape[:-1] + (out.shape[1],))
+
+
+def dequantize_q8_0(w, k):
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    rows = w.reshape(-1, w.shape[-1])
+    out = np.zeros((rows.shape[0], k), dtype=np.float32)
+    for r in range(rows.shape[0]):
+        lib().zo_dequantize_row_q8_0(_p(rows[r]), _p(out[r]), C.c_int64(k))
+    return out.reshape(w.shape[:-1] + (k,))
+
+
+def matmul_q8_0(x, w, S, I, O):
+    """y[S, O] = x[S, I] . W^T with W packed rows of Q8_0 blocks, activations quantised to Q8_0"""
+    x = _f32(x)
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    y = np.zeros((S, O), dtype=np.float32)
+    lib().zo_matmul_q8_0(_p(y), _p(x), _p(w), C.c_int(S), C.c_int(I), C.c_int(O))
     return y
 
 

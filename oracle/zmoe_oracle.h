@@ -72,6 +72,14 @@ float zo_vec_dot_q8_K(int type, int n, const void *w, const void *q8);
  * with the ggml-cpu arithmetic. */
 void zo_matmul(int type, float *y, const float *x, const void *w, int S, int I, int O);
 
+/* Dense Q8_0 (zmoe_oracle_dense.c): 34-byte blocks {fp16 d; int8 qs[32]}; activations quantised to
+ * Q8_0 as ggml's CPU MUL_MAT does (rule restated there; parity unpinned). */
+uint16_t zo_fp32_to_fp16(float f);
+void zo_quantize_row_q8_0(const float *x, void *y, int64_t k);
+void zo_dequantize_row_q8_0(const void *w, float *y, int64_t k);
+float zo_vec_dot_q8_0_q8_0(int n, const void *w, const void *x);
+void zo_matmul_q8_0(float *y, const float *x, const void *w, int S, int I, int O);
+
 /* MUL_MAT_ID (reference models/graph/moe_routed_ggml.hpp:181-193,
  * kernels/quant/kquant_matmul.cu:647-662 for the id rules):
  *   y[t,k,:] = W[ids[t,k]] . x[t, x_per_route ? k : 0, :]

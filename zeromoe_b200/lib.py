@@ -29,6 +29,8 @@ EXPORTS = [
     "zmoe_debug_gemm_cycles",
     "zmoe_ep_unique_id", "zmoe_ep_comm_init", "zmoe_ep_comm_destroy", "zmoe_ep_create", "zmoe_ep_destroy",
     "zmoe_ep_forward", "zmoe_ep_forward_routed", "zmoe_ep_last_rows",
+    "launch_q8_0_matmul", "launch_q8_0_matmul_stream", "launch_rmsnorm",
+    "zmoe_decoder_create", "zmoe_decoder_destroy", "zmoe_decoder_reset", "zmoe_decoder_step", "zmoe_decoder_read",
 ]
 
 
@@ -49,6 +51,15 @@ class LayerDesc(C.Structure):
                 ("gating", C.c_int), ("weights_norm", C.c_int), ("weights_scale", C.c_float),
                 ("n_groups", C.c_int), ("n_groups_used", C.c_int),
                 ("swiglu_clamp", C.c_float), ("swiglu_clamp_fused", C.c_int)]
+
+
+class DecoderDesc(C.Structure):
+    _fields_ = [("n_layers", C.c_int), ("d_model", C.c_int), ("n_heads", C.c_int), ("n_kv_heads", C.c_int),
+                ("head_dim", C.c_int), ("vocab", C.c_int), ("max_ctx", C.c_int), ("max_tokens", C.c_int),
+                ("rms_eps", C.c_float), ("rope_theta", C.c_float),
+                ("attn_norm_w", C.POINTER(C.c_void_p)), ("wqkv", C.POINTER(C.c_void_p)), ("wo", C.POINTER(C.c_void_p)),
+                ("ffn_norm_w", C.POINTER(C.c_void_p)), ("moe", C.POINTER(C.c_void_p)),
+                ("tok_embd", C.c_void_p), ("out_norm_w", C.c_void_p), ("lm_head", C.c_void_p)]
 
 
 class Tensor(C.Structure):
@@ -125,6 +136,18 @@ def load():
     L.zmoe_ep_forward.argtypes = [vp, vp, vp, vp, vp, vp, i, vp]
     L.zmoe_ep_forward_routed.argtypes = [vp, vp, vp, i, vp, vp, vp, vp, i, vp]
     L.zmoe_ep_last_rows.argtypes = [vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+    L.launch_q8_0_matmul.argtypes = [vp, vp, vp, i, i, i]
+    L.launch_q8_0_matmul.restype = None
+    L.launch_q8_0_matmul_stream.argtypes = [vp, vp, vp, i, i, i, vp]
+    L.launch_q8_0_matmul_stream.restype = None
+    L.launch_rmsnorm.argtypes = [vp, vp, vp, i, i, f]
+    L.launch_rmsnorm.restype = None
+    L.zmoe_decoder_create.argtypes = [C.POINTER(DecoderDesc), C.POINTER(vp)]
+    L.zmoe_decoder_destroy.argtypes = [vp]
+    L.zmoe_decoder_destroy.restype = None
+    L.zmoe_decoder_reset.argtypes = [vp, vp]
+    L.zmoe_decoder_step.argtypes = [vp, vp, i, vp]
+    L.zmoe_decoder_read.argtypes = [vp, vp, vp, vp, i]
     _lib = L
     return L
 
@@ -281,6 +304,69 @@ class Layer:
             self.close()
         except Exception:
             pass
+
+
+class Decoder:
+    """A decoder over borrowed device tensors (zmoe_decoder).  layers: list of dicts with attn_norm [D] f32, wqkv
+    and wo (uint8 Q8_0 rows), ffn_norm [D] f32 and moe (a Layer on a context of >= max_tokens tokens)."""
+
+    def __init__(self, layers, tok_embd, out_norm, lm_head, d_model, n_heads, n_kv_heads, head_dim, vocab, max_ctx,
+                 max_tokens, rms_eps=1e-6, rope_theta=10000.0):
+        self.keep = (layers, tok_embd, out_norm, lm_head)
+        n = len(layers)
+        arr = lambda key: (C.c_void_p * n)(*[l[key].data_ptr() for l in layers])
+        self._arrays = [arr("attn_norm"), arr("wqkv"), arr("wo"), arr("ffn_norm"),
+                        (C.c_void_p * n)(*[l["moe"].h.value for l in layers])]
+        d = DecoderDesc()
+        d.n_layers, d.d_model, d.n_heads, d.n_kv_heads, d.head_dim = n, d_model, n_heads, n_kv_heads, head_dim
+        d.vocab, d.max_ctx, d.max_tokens = vocab, max_ctx, max_tokens
+        d.rms_eps, d.rope_theta = rms_eps, rope_theta
+        d.attn_norm_w, d.wqkv, d.wo, d.ffn_norm_w, d.moe = [C.cast(a, C.POINTER(C.c_void_p)) for a in self._arrays]
+        d.tok_embd, d.out_norm_w, d.lm_head = tok_embd.data_ptr(), out_norm.data_ptr(), lm_head.data_ptr()
+        self.desc = d
+        self.vocab = vocab
+        self.h = C.c_void_p()
+        check(load().zmoe_decoder_create(C.byref(d), C.byref(self.h)), "zmoe_decoder_create")
+
+    def reset(self, stream=None):
+        check(load().zmoe_decoder_reset(self.h, _stream_ptr(stream)), "zmoe_decoder_reset")
+
+    def step(self, tokens=None, stream=None):
+        """tokens: int32 device tensor [T], or None = continue with the token the last step sampled"""
+        T = 1 if tokens is None else tokens.shape[0]
+        check(load().zmoe_decoder_step(self.h, ptr(tokens), T, _stream_ptr(stream)), "zmoe_decoder_step")
+
+    def read(self, n_logits=0):
+        """(next token, position, logits[:n_logits]) after a synchronisation"""
+        import torch
+        torch.cuda.synchronize()
+        tok, pos = C.c_int32(), C.c_int32()
+        lg = np.zeros(max(n_logits, 1), dtype=np.float32)
+        check(load().zmoe_decoder_read(self.h, C.byref(tok), C.byref(pos), lg.ctypes.data_as(C.c_void_p), n_logits),
+              "zmoe_decoder_read")
+        return tok.value, pos.value, lg[:n_logits]
+
+    def close(self):
+        if self.h:
+            load().zmoe_decoder_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def q8_0_matmul(x, w, O, stream=None):
+    """y[S, O] = x[S, I] . W^T, W uint8 rows of Q8_0 blocks (launch_q8_0_matmul_stream)"""
+    import torch
+    S, I = x.shape
+    y = torch.empty((S, O), dtype=torch.float32, device=x.device)
+    L = load()
+    L.launch_q8_0_matmul_stream(ptr(y), ptr(x), ptr(w), S, I, O, _stream_ptr(stream))
+    check(L.zmoe_last_status(), "launch_q8_0_matmul_stream")
+    return y
 
 
 def dense_matmul(qtype, x, w, O, stream=None):
