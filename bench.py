@@ -20,7 +20,8 @@ Further keys report the other benchmark configurations on the same GPUs: `sweep`
 (batches 1 / 4 / 16 / 64 of the stack), `cfg1` (one Q4_K layer 2048 / 768, 1 and 64
 tokens), `prefill` (IQ2_XXS, 4096 tokens, Zipf-skewed load, tensor-core grouped
 GEMM), `cfg4` (DeepSeek-V3-shaped layer, 256 experts + shared expert, 64 and 8192
-tokens) and, with N > 1, `strong` (the stack at a fixed global batch of 128).
+tokens), `cfg5` (the full 48-layer decoder: prompt of 512 tokens, 256 greedy steps, one GPU) and, with N > 1,
+`strong` (the stack at a fixed global batch of 128).
 
 With N > 1 (torchrun) the experts of every layer are sharded over the ranks
 (expert parallel).  The headline keeps every rank's T tokens (weak scaling);
@@ -499,6 +500,103 @@ def run_case(lib, tm, cfg, seed, dev, rank, world, tokens_global, steps, warmup=
     return res
 
 
+CFG5 = dict(name="full random-init MoE decoder: 48 layers, hidden 2048, GQA 32 query / 4 KV heads of 128, RoPE, f16 KV "
+                 "cache (4096 positions), 128 experts top-8 ffn 768 Q4_K, Q8_0 attention and output head, vocab 151552; "
+                 "prompt 512 tokens, 256 generated",
+            layers=48, D=2048, H=32, KV=4, hd=128, F=768, E=128, K=8, V=151552, ctx=4096, prompt=512, gen=256)
+
+
+def q8_0_rows(rows, cols, gen, device, d_sigma):
+    """uint8 [rows, cols / 32 * 34]: random int8 quants, fp16 scales |N(0, d_sigma)|"""
+    import torch
+    nb = rows * (cols // 32)
+    blk = torch.randint(0, 256, (nb, 34), dtype=torch.uint8, device=device, generator=gen)
+    h = (torch.randn(nb, device=device, generator=gen) * d_sigma).abs().to(torch.float16)
+    blk[:, 0:2] = h.view(torch.uint8).reshape(nb, 2)
+    return blk.reshape(rows, -1)
+
+
+def run_decoder_case(lib, dev, seed, peaks, cfg=CFG5):
+    """The fifth configuration on one GPU: the prompt in one step, then `gen` greedy steps of one token each, the
+    sampled token and the position staying on the device (a step captured once as a CUDA graph and replayed).
+    Reports decode tokens/s and the HBM fraction of the bytes a decode step has to stream."""
+    import torch
+    c = cfg
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed * 101 + 5)
+    D, F, E, K, H, KV, hd, V = c["D"], c["F"], c["E"], c["K"], c["H"], c["KV"], c["hd"], c["V"]
+    ctx = lib.Context(c["prompt"], D, F, E, K)
+    layers = []
+    for l in range(c["layers"]):
+        wg = torch_blocks(Q4_K, E * F * (D // 256), gen, dev).reshape(E, F, -1)
+        wu = torch_blocks(Q4_K, E * F * (D // 256), gen, dev).reshape(E, F, -1)
+        wd = torch_blocks(Q4_K, E * D * (F // 256), gen, dev).reshape(E, D, -1)
+        wr = torch.randn((E, D), device=dev, generator=gen) * 0.02
+        moe = lib.Layer(ctx, D, F, E, K, (Q4_K,) * 3, wg, wu, wd, router_w=wr)
+        layers.append(dict(attn_norm=torch.ones(D, device=dev), ffn_norm=torch.ones(D, device=dev),
+                           wqkv=q8_0_rows((H + 2 * KV) * hd, D, gen, dev, 2e-4), wo=q8_0_rows(D, H * hd, gen, dev, 2e-4),
+                           moe=moe, keep=(wg, wu, wd, wr)))
+    embd = q8_0_rows(V, D, gen, dev, 0.01)
+    head = q8_0_rows(V, D, gen, dev, 2e-4)
+    dec = lib.Decoder(layers, embd, torch.ones(D, device=dev), head, D, H, KV, hd, V, max_ctx=c["ctx"],
+                      max_tokens=c["prompt"])
+    prompt = torch.randint(0, V, (c["prompt"],), dtype=torch.int32, device=dev, generator=gen)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    dec.step(prompt)                       # warm-up of the prompt path
+    dec.reset()
+    torch.cuda.synchronize()
+    ev[0].record()
+    dec.step(prompt)
+    ev[1].record()
+    torch.cuda.synchronize()
+    ctx.check()
+    prefill_ms = ev[0].elapsed_time(ev[1])
+    # one decode step as a graph; the position and the token live on the device, so replays continue the sequence
+    for _ in range(3):
+        dec.step()
+    torch.cuda.synchronize()
+    graph, launch = None, "eager"
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            dec.step()
+        launch = "cuda graph replay"
+    except Exception as exc:
+        graph = None
+        sys.stderr.write("decoder step capture failed, timing eager launches: %r\n" % (exc,))
+    dec.reset()
+    dec.step(prompt)
+    torch.cuda.synchronize()
+    toks = []
+    ev[2].record()
+    for i in range(c["gen"]):
+        if graph is not None:
+            graph.replay()
+        else:
+            dec.step()
+    ev[3].record()
+    torch.cuda.synchronize()
+    ctx.check()
+    tok, pos, lg = dec.read(64)
+    decode_ms = ev[2].elapsed_time(ev[3])
+    eb = F * row_bytes(Q4_K, D) * 2 + D * row_bytes(Q4_K, F)
+    attn_b = ((H + 2 * KV) * hd + D) * (D // 32) * 34 if H * hd == D else ((H + 2 * KV) * hd * (D // 32) + D * (H * hd // 32)) * 34
+    kv_b = 2 * (c["prompt"] + c["gen"] / 2) * KV * hd * 2
+    per_tok = c["layers"] * (K * eb + attn_b + E * D * 4 + kv_b) + V * (D // 32) * 34
+    res = {"workload": c["name"], "decode_tokens_per_s": c["gen"] / (decode_ms * 1e-3), "ms_per_token": decode_ms / c["gen"],
+           "prompt_ms": prefill_ms, "prompt_tokens_per_s": c["prompt"] / (prefill_ms * 1e-3), "launch": launch,
+           "bytes_per_token": per_tok, "frac_of_hbm_peak": per_tok / (decode_ms / c["gen"] * 1e-3) / 1e9 / peaks["hbm_gbs"],
+           "final_position": pos, "last_token": tok, "logits_finite": bool(np.isfinite(lg).all()),
+           "check": "tokens in range and logits finite; parity of the step against the CPU restatement is tested at "
+                    "small shapes (tests/test_gpu_decoder.py)",
+           "n_gpus_note": "one GPU; the decoder step has no expert-parallel form yet"}
+    assert pos == c["prompt"] + c["gen"] and 0 <= tok < V
+    dec.close()
+    del dec, layers, embd, head
+    torch.cuda.empty_cache()
+    return res
+
+
 def gemm_cycles(lib, calls):
     """per-role cycle sums of the grouped GEMM's CTA 0 (only a profiling build of the library has them)"""
     import ctypes as C
@@ -765,6 +863,10 @@ def main():
             strong = run_case(lib, tm, CFG2, args.seed, dev, rank, world, 128, extra_steps, peaks=peaks)
             strong["note"] = "the 8-layer stack at a fixed global batch of 128 tokens (strong scaling)"
 
+    cfg5 = None
+    if world == 1 and not args.no_sweep and LAYERS == 8:
+        cfg5 = run_decoder_case(lib, dev, args.seed, peaks)
+
     # ---- CPU baseline on a bounded sample -----------------------------------------------
     cpu = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
@@ -793,7 +895,7 @@ def main():
                           "exchange": None if world == 1 else "all-gather / reduce-scatter (small batch)"},
                 "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "roofline": roofline,
                 "layer_stack_roofline": layer_roofline, "max_abs_err_rel_to_norm": err_main, "sweep": sweep,
-                "cfg1": cfg1, "prefill": prefill, "cfg4": cfg4, "strong": strong, "cpu_baseline": cpu}
+                "cfg1": cfg1, "prefill": prefill, "cfg4": cfg4, "cfg5": cfg5, "strong": strong, "cpu_baseline": cpu}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

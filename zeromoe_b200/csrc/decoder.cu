@@ -224,22 +224,28 @@ __global__ void rope_kv_kernel(float *__restrict__ qkv, __half *__restrict__ kc,
 }
 
 // ---------------------------------------------------------------------------
-// Grouped-query attention over the f16 cache, causal.  grid (T, KV); one warp per query head of the group.
+// Grouped-query attention over the f16 cache, causal, keys split over CTAs.  grid (T, KV, NS); one warp per
+// query head of the group.  Split z of a token takes the z-th share of its keys and leaves a partial
+// (running maximum, sum of weights, weighted sum of V) in scratch; attention_merge_kernel combines the shares.
 // A lane owns one key of a 32-key chunk for the scores (the whole head_dim dot product, K row read as 16-byte
 // pieces) and DPL output dimensions for the weighted sum of V; the softmax is the running-maximum form.
 // ---------------------------------------------------------------------------
+constexpr int ATTN_SPLITS = 16;
 template <int HD>
 __global__ void __launch_bounds__(1024) attention_kernel(const float *__restrict__ qkv, const __half *__restrict__ kc,
-                                                         const __half *__restrict__ vc, float *__restrict__ out,
+                                                         const __half *__restrict__ vc, float *__restrict__ part,
                                                          const int *__restrict__ pos, int H, int KV, float scale,
                                                          int max_ctx) {
     constexpr int DPL = HD / 32;
     extern __shared__ float q_s[];          // [warps][HD]
     pdl_wait_prior_grid();
     pdl_launch_dependents();
-    const int t = blockIdx.x, kvh = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x, kvh = blockIdx.y, z = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = H / KV, h = kvh * G + warp;
     const int n_keys = min(*pos + t + 1, max_ctx);
+    // this split's keys: whole chunks of 32, shared out evenly
+    const int chunks = (n_keys + 31) / 32, per = (chunks + ATTN_SPLITS - 1) / ATTN_SPLITS;
+    const int key_lo = min(n_keys, z * per * 32), key_hi = min(n_keys, (z + 1) * per * 32);
     const int ld = (H + 2 * KV) * HD;
     float *qs = q_s + warp * HD;
     for (int i = lane; i < HD; i += 32) qs[i] = qkv[(size_t)t * ld + (size_t)h * HD + i];
@@ -247,10 +253,10 @@ __global__ void __launch_bounds__(1024) attention_kernel(const float *__restrict
     float m = -CUDART_INF_F, l = 0.f, acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
-    for (int k0 = 0; k0 < n_keys; k0 += 32) {
+    for (int k0 = key_lo; k0 < key_hi; k0 += 32) {
         const int key = k0 + lane;
         float s = -CUDART_INF_F;
-        if (key < n_keys) {
+        if (key < key_hi) {
             const uint4 *kr = reinterpret_cast<const uint4 *>(kc + ((size_t)key * KV + kvh) * HD);
             float dot = 0.f;
 #pragma unroll
@@ -271,14 +277,14 @@ __global__ void __launch_bounds__(1024) attention_kernel(const float *__restrict
         for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
         const float m_new = fmaxf(m, cm);
         const float corr = expf(m - m_new);          // 0 on the first chunk (m = -inf)
-        const float pr = key < n_keys ? expf(s - m_new) : 0.f;
+        const float pr = key < key_hi ? expf(s - m_new) : 0.f;
         float ps = pr;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
         l = l * corr + ps;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) acc[i] *= corr;
-        const int nk = min(32, n_keys - k0);
+        const int nk = min(32, key_hi - k0);
         for (int j = 0; j < nk; ++j) {
             const float pj = __shfl_sync(0xffffffffu, pr, j);
             const __half *vr = vc + ((size_t)(k0 + j) * KV + kvh) * HD + DPL * lane;
@@ -295,9 +301,39 @@ __global__ void __launch_bounds__(1024) attention_kernel(const float *__restrict
         }
         m = m_new;
     }
+    // partial of (t, h, z): [HD values | m | l]
+    float *pp = part + (((size_t)t * H + h) * ATTN_SPLITS + z) * (HD + 2);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) pp[DPL * lane + i] = acc[i];
+    if (lane == 0) { pp[HD] = m; pp[HD + 1] = l; }
+}
+
+// out[t, h, :] = sum_z w_z * acc_z / sum_z w_z * l_z with w_z = exp(m_z - max m); one warp per (t, h); shares are
+// added in ascending z (empty shares have l = 0 and m = -inf)
+template <int HD>
+__global__ void __launch_bounds__(256) attention_merge_kernel(const float *__restrict__ part, float *__restrict__ out, int TH) {
+    constexpr int DPL = HD / 32;
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int th = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (th >= TH) return;
+    const float *pp = part + (size_t)th * ATTN_SPLITS * (HD + 2);
+    float mx = -CUDART_INF_F;
+    for (int z = 0; z < ATTN_SPLITS; ++z) mx = fmaxf(mx, pp[z * (HD + 2) + HD]);
+    float l = 0.f, acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+    for (int z = 0; z < ATTN_SPLITS; ++z) {
+        const float lz = pp[z * (HD + 2) + HD + 1];
+        if (lz == 0.f) continue;
+        const float wz = expf(pp[z * (HD + 2) + HD] - mx);
+        l = fmaf(wz, lz, l);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(wz, pp[z * (HD + 2) + DPL * lane + i], acc[i]);
+    }
     const float inv = 1.0f / l;
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) out[(size_t)t * H * HD + (size_t)h * HD + DPL * lane + i] = acc[i] * inv;
+    for (int i = 0; i < DPL; ++i) out[(size_t)th * HD + DPL * lane + i] = acc[i] * inv;
 }
 
 // arg-max of a row, lowest index on ties (greedy sampling); one CTA
@@ -393,7 +429,7 @@ struct zmoe_decoder {
     std::vector<const void *> wqkv, wo;
     std::vector<zmoe_layer *> moe;
     int qkv_cols = 0;
-    float *h = nullptr, *xn = nullptr, *qkv = nullptr, *ao = nullptr, *logits = nullptr;
+    float *h = nullptr, *xn = nullptr, *qkv = nullptr, *ao = nullptr, *logits = nullptr, *apart = nullptr;
     int8_t *aq = nullptr;
     float *ad = nullptr;
     __half *kc = nullptr, *vc = nullptr;     // [layers][max_ctx][KV * hd]
@@ -438,7 +474,7 @@ void launch_q8_0_matmul(float *y, const float *x, const void *weights, int S, in
 
 void zmoe_decoder_destroy(zmoe_decoder *dec) {
     if (!dec) return;
-    cudaFree(dec->h); cudaFree(dec->xn); cudaFree(dec->qkv); cudaFree(dec->ao); cudaFree(dec->logits);
+    cudaFree(dec->h); cudaFree(dec->xn); cudaFree(dec->qkv); cudaFree(dec->ao); cudaFree(dec->logits); cudaFree(dec->apart);
     cudaFree(dec->aq); cudaFree(dec->ad); cudaFree(dec->kc); cudaFree(dec->vc); cudaFree(dec->pos); cudaFree(dec->next);
     delete dec;
 }
@@ -475,6 +511,7 @@ int zmoe_decoder_create(const zmoe_decoder_desc *desc, zmoe_decoder **out) {
     int bad = 0;
     bad |= A(&dec->h, T * D); bad |= A(&dec->xn, T * D); bad |= A(&dec->qkv, T * dec->qkv_cols); bad |= A(&dec->ao, T * QO);
     bad |= A(&dec->logits, (size_t)d.vocab);
+    bad |= A(&dec->apart, T * d.n_heads * ATTN_SPLITS * (d.head_dim + 2));
     bad |= A(&dec->aq, T * widest); bad |= A(&dec->ad, T * widest / 32);
     bad |= A(&dec->kc, kv); bad |= A(&dec->vc, kv);
     bad |= A(&dec->pos, 1); bad |= A(&dec->next, 1);
@@ -518,16 +555,20 @@ int zmoe_decoder_step(zmoe_decoder *dec, const int32_t *tokens_dev, int T, void 
         if (!rc) {
             const int warps = H / KV;
             const size_t smem = (size_t)warps * hd * sizeof(float);
-            if (hd == 128)
-                rc = cu(launch_pdl(attention_kernel<128>, dim3(T, KV), dim3(32 * warps), smem, st, (const float *)dec->qkv,
-                                   (const __half *)(dec->kc + l * kv_layer), (const __half *)(dec->vc + l * kv_layer), dec->ao,
-                                   (const int *)dec->pos, H, KV, scale, d.max_ctx));
-            else
-                rc = cu(launch_pdl(attention_kernel<64>, dim3(T, KV), dim3(32 * warps), smem, st, (const float *)dec->qkv,
-                                   (const __half *)(dec->kc + l * kv_layer), (const __half *)(dec->vc + l * kv_layer), dec->ao,
-                                   (const int *)dec->pos, H, KV, scale, d.max_ctx));
+            const __half *kl = dec->kc + l * kv_layer, *vl = dec->vc + l * kv_layer;
+            if (hd == 128) {
+                rc = cu(launch_pdl(attention_kernel<128>, dim3(T, KV, ATTN_SPLITS), dim3(32 * warps), smem, st,
+                                   (const float *)dec->qkv, kl, vl, dec->apart, (const int *)dec->pos, H, KV, scale, d.max_ctx));
+                if (!rc) rc = cu(launch_pdl(attention_merge_kernel<128>, dim3((T * H + 7) / 8), dim3(256), 0, st,
+                                            (const float *)dec->apart, dec->ao, T * H));
+            } else {
+                rc = cu(launch_pdl(attention_kernel<64>, dim3(T, KV, ATTN_SPLITS), dim3(32 * warps), smem, st,
+                                   (const float *)dec->qkv, kl, vl, dec->apart, (const int *)dec->pos, H, KV, scale, d.max_ctx));
+                if (!rc) rc = cu(launch_pdl(attention_merge_kernel<64>, dim3((T * H + 7) / 8), dim3(256), 0, st,
+                                            (const float *)dec->apart, dec->ao, T * H));
+            }
         }
-        count_launches(2);
+        count_launches(3);
         if (!rc) rc = launch_quantize_q8_0(dec->ao, QO, dec->aq, dec->ad, T, QO, st);
         if (!rc) rc = launch_q8_0_mm(dec->h, D, dec->wo[l], dec->aq, dec->ad, T, QO, D, 1, st);
         // ---- MoE block: h += MoE(rmsnorm(h)) ----
