@@ -337,7 +337,49 @@ int zmoe_decoder_step(zmoe_decoder *dec, const int32_t *tokens_dev, int T, void 
 int zmoe_decoder_read(zmoe_decoder *dec, int32_t *next_token_host, int32_t *pos_host, float *logits_host, int n_logits);
 
 /* =========================================================================
- * 6. Parity hooks -- expose the integer stages so tests can compare them
+ * 6. Weight ingest -- the conversion between the expert-major [gate|up|down] slab the reference keeps in host
+ *    memory and the three planar tensors of its ggml graphs (same signatures and meaning as the reference's
+ *    launchers, with the status returned as int = cudaError_t and the stream as void*), and a reader of the
+ *    GGUF container that finds a layer's expert tensors (blk.N.ffn_{gate,up,down}_exps.weight, the names and
+ *    type ids of reference models/base/gguf_loader.hpp:28-51).  The layer entry of section 3 reads slabs in
+ *    place through zmoe_weight.expert_stride, so the unpack is for hosts that keep planar tensors.
+ * ========================================================================= */
+/* replaces reference kernels/math/ggml_moe_pack.cu:122-149: record i of `src` (count records, src_stride bytes apart,
+ * each gate bytes | up bytes | down bytes) goes to expert i of the planar tensors */
+int launch_ggml_moe_unpack(const void *src, void *gate, void *up, void *down, int count, size_t src_stride,
+                           size_t gate_bytes, size_t up_bytes, size_t down_bytes, size_t gate_stride, size_t up_stride,
+                           size_t down_stride, void *stream);
+/* replaces reference kernels/math/ggml_moe_pack.cu:151-179: record i goes to expert dst_slots[i] (negative: skipped) */
+int launch_ggml_moe_unpack_scatter(const void *src, void *gate, void *up, void *down, const int32_t *dst_slots, int count,
+                                   size_t src_stride, size_t gate_bytes, size_t up_bytes, size_t down_bytes,
+                                   size_t gate_stride, size_t up_stride, size_t down_stride, void *stream);
+/* the opposite direction (no counterpart in the reference, which packs on the host) */
+int zmoe_moe_pack(void *slab, const void *gate, const void *up, const void *down, int count, size_t slab_stride,
+                  size_t gate_bytes, size_t up_bytes, size_t down_bytes, size_t gate_stride, size_t up_stride,
+                  size_t down_stride, void *stream);
+
+typedef struct zmoe_gguf zmoe_gguf;
+typedef struct zmoe_gguf_tensor {
+    int type;              /* GGUF / ggml type id */
+    int n_dims;
+    int64_t ne[4];         /* elements per dimension, ne[0] the row length */
+    uint64_t file_offset;  /* of the tensor's first byte in the file */
+    uint64_t bytes;
+} zmoe_gguf_tensor;
+/* GGUF versions 2 and 3; host-side, no device needed */
+int zmoe_gguf_open(const char *path, zmoe_gguf **out);
+void zmoe_gguf_close(zmoe_gguf *g);
+int zmoe_gguf_tensor_count(zmoe_gguf *g);
+/* ZMOE_ERR_STATE when the file has no tensor of that name */
+int zmoe_gguf_find(zmoe_gguf *g, const char *name, zmoe_gguf_tensor *out);
+int zmoe_gguf_read(zmoe_gguf *g, const zmoe_gguf_tensor *t, void *dst_host, uint64_t first_byte, uint64_t n_bytes);
+/* copies blk.<layer>.ffn_{gate,up,down}_exps.weight to the three device buffers (planar, experts back to back);
+ * info3, when given, receives the three tensors' descriptions; synchronises `stream` */
+int zmoe_gguf_load_experts(zmoe_gguf *g, int layer, void *gate_dev, void *up_dev, void *down_dev, zmoe_gguf_tensor *info3,
+                           void *stream);
+
+/* =========================================================================
+ * 7. Parity hooks -- expose the integer stages so tests can compare them
  *    bit-for-bit with the CPU path.
  * ========================================================================= */
 /* x_dev [rows, I] f32 -> blocks_dev: rows * I/256 ggml Q8_K blocks of 292 bytes

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libzmoe_b200.so")
-SOURCES = ["api.cu", "mmid.cu", "kernels_misc.cu", "noalloc.cu", "gemm_sm100.cu", "ep.cu", "decoder.cu"]
+SOURCES = ["api.cu", "mmid.cu", "kernels_misc.cu", "noalloc.cu", "gemm_sm100.cu", "ep.cu", "decoder.cu", "ingest.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]

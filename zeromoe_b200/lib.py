@@ -31,6 +31,8 @@ EXPORTS = [
     "zmoe_ep_forward", "zmoe_ep_forward_routed", "zmoe_ep_last_rows",
     "launch_q8_0_matmul", "launch_q8_0_matmul_stream", "launch_rmsnorm",
     "zmoe_decoder_create", "zmoe_decoder_destroy", "zmoe_decoder_reset", "zmoe_decoder_step", "zmoe_decoder_read",
+    "launch_ggml_moe_unpack", "launch_ggml_moe_unpack_scatter", "zmoe_moe_pack", "zmoe_gguf_open", "zmoe_gguf_close",
+    "zmoe_gguf_tensor_count", "zmoe_gguf_find", "zmoe_gguf_read", "zmoe_gguf_load_experts",
 ]
 
 
@@ -60,6 +62,11 @@ class DecoderDesc(C.Structure):
                 ("attn_norm_w", C.POINTER(C.c_void_p)), ("wqkv", C.POINTER(C.c_void_p)), ("wo", C.POINTER(C.c_void_p)),
                 ("ffn_norm_w", C.POINTER(C.c_void_p)), ("moe", C.POINTER(C.c_void_p)),
                 ("tok_embd", C.c_void_p), ("out_norm_w", C.c_void_p), ("lm_head", C.c_void_p)]
+
+
+class GgufTensor(C.Structure):
+    _fields_ = [("type", C.c_int), ("n_dims", C.c_int), ("ne", C.c_int64 * 4), ("file_offset", C.c_uint64),
+                ("bytes", C.c_uint64)]
 
 
 class Tensor(C.Structure):
@@ -148,6 +155,17 @@ def load():
     L.zmoe_decoder_reset.argtypes = [vp, vp]
     L.zmoe_decoder_step.argtypes = [vp, vp, i, vp]
     L.zmoe_decoder_read.argtypes = [vp, vp, vp, vp, i]
+    sz = C.c_size_t
+    L.launch_ggml_moe_unpack.argtypes = [vp, vp, vp, vp, i, sz, sz, sz, sz, sz, sz, sz, vp]
+    L.launch_ggml_moe_unpack_scatter.argtypes = [vp, vp, vp, vp, vp, i, sz, sz, sz, sz, sz, sz, sz, vp]
+    L.zmoe_moe_pack.argtypes = [vp, vp, vp, vp, i, sz, sz, sz, sz, sz, sz, sz, vp]
+    L.zmoe_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    L.zmoe_gguf_close.argtypes = [vp]
+    L.zmoe_gguf_close.restype = None
+    L.zmoe_gguf_tensor_count.argtypes = [vp]
+    L.zmoe_gguf_find.argtypes = [vp, C.c_char_p, C.POINTER(GgufTensor)]
+    L.zmoe_gguf_read.argtypes = [vp, C.POINTER(GgufTensor), vp, C.c_uint64, C.c_uint64]
+    L.zmoe_gguf_load_experts.argtypes = [vp, i, vp, vp, vp, C.POINTER(GgufTensor), vp]
     _lib = L
     return L
 
