@@ -203,6 +203,10 @@ int zmoe_route(zmoe_layer *layer, const float *x_dev, int T, void *stream);
  * negative ids are inactive routes */
 int zmoe_set_routes(zmoe_layer *layer, const float *x_dev, const int32_t *ids_dev, const float *weights_dev, int T,
                     void *stream);
+/* the same with the rows of ids and weights a given number of bytes apart (multiples of 4, >= topk * 4): ggml's
+ * top-k ids are a view [topk, T] of the argsort result whose rows are n_experts * 4 bytes apart */
+int zmoe_set_routes_strided(zmoe_layer *layer, const float *x_dev, const int32_t *ids_dev, size_t ids_token_stride,
+                            const float *weights_dev, size_t weights_token_stride, int T, void *stream);
 /* the same for a layer that holds the experts [first_expert, first_expert + n_experts) of a larger
  * model (one rank of an expert-parallel group): ids are the model's expert numbers, the ones outside
  * the layer's window become inactive routes.  Same convention as the reference's hot / cold branch

@@ -346,7 +346,7 @@ int zmoe_route(zmoe_layer *L, const float *x_dev, int T, void *stream) {
 }
 
 static int set_routes_impl(zmoe_layer *L, const float *x_dev, const int32_t *ids_dev, const float *weights_dev, int T,
-                           int first_expert, bool window, void *stream) {
+                           int first_expert, bool window, void *stream, int ids_ld = 0, int w_ld = 0) {
     if (!L || !x_dev || !ids_dev || !weights_dev || T <= 0) return ZMOE_ERR_ARG;
     zmoe_ctx *c = L->ctx;
     if (T > c->max_t) return ZMOE_ERR_CAPACITY;
@@ -358,7 +358,7 @@ static int set_routes_impl(zmoe_layer *L, const float *x_dev, const int32_t *ids
     // the planner takes the routes in (copy, window mapping) before it groups them: one launch
     if (!rc)
         rc = launch_plan_ingest(ids_dev, weights_dev, c->ids, c->weights, (int)P, L->d.n_experts, first_expert, window,
-                                c->plan.b, L->nrt_gu, L->nrt_dn, st);
+                                c->plan.b, L->nrt_gu, L->nrt_dn, st, ids_ld ? L->d.topk : 0, ids_ld, w_ld);
     if (!rc) { g_launches += 1; c->routed_t = T; c->x_last = x_dev; }
     return rc;
 }
@@ -372,6 +372,17 @@ int zmoe_set_routes_window(zmoe_layer *L, const float *x_dev, const int32_t *ids
                            int first_expert, void *stream) {
     if (first_expert < 0) return ZMOE_ERR_ARG;
     return set_routes_impl(L, x_dev, ids_dev, weights_dev, T, first_expert, true, stream);
+}
+
+int zmoe_set_routes_strided(zmoe_layer *L, const float *x_dev, const int32_t *ids_dev, size_t ids_token_stride,
+                            const float *weights_dev, size_t weights_token_stride, int T, void *stream) {
+    if (!L) return ZMOE_ERR_ARG;
+    const size_t k4 = (size_t)L->d.topk * 4;
+    if (ids_token_stride % 4 || weights_token_stride % 4 || ids_token_stride < k4 || weights_token_stride < k4 ||
+        ids_token_stride / 4 > INT32_MAX || weights_token_stride / 4 > INT32_MAX)
+        return ZMOE_ERR_ALIGN;
+    return set_routes_impl(L, x_dev, ids_dev, weights_dev, T, 0, false, stream, (int)(ids_token_stride / 4),
+                           (int)(weights_token_stride / 4));
 }
 
 int zmoe_expert_ffn(zmoe_layer *L, float *out_dev, int T, int accumulate, void *stream) {

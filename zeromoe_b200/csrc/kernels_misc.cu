@@ -232,6 +232,8 @@ struct RouteIngest {
     float *dst_w = nullptr;
     int first = 0;
     int window = 0;      // 0: ids are copied unchanged
+    int topk = 0;        // > 0: the source rows are ids_ld / w_ld elements apart (a view of a wider table)
+    int ids_ld = 0, w_ld = 0;
 };
 
 __global__ void __launch_bounds__(1024) plan_from_ids_kernel(const int32_t *ids, int P, int E, PlanOut po, RouteIngest in) {
@@ -240,9 +242,10 @@ __global__ void __launch_bounds__(1024) plan_from_ids_kernel(const int32_t *ids,
     pdl_launch_dependents();
     if (in.src_ids) {
         for (int p = threadIdx.x; p < P; p += blockDim.x) {
-            const int e = in.src_ids[p];
+            const int t = in.topk > 0 ? p / in.topk : 0, k = in.topk > 0 ? p - t * in.topk : p;
+            const int e = in.src_ids[(size_t)t * in.ids_ld + k];
             in.dst_ids[p] = !in.window ? e : (e >= in.first && e < in.first + E) ? e - in.first : -1;
-            in.dst_w[p] = in.src_w[p];
+            in.dst_w[p] = in.src_w[(size_t)t * in.w_ld + k];
         }
         __syncthreads();
     }
@@ -266,9 +269,11 @@ int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &pl
 }
 
 int launch_plan_ingest(const int32_t *src_ids, const float *src_w, int32_t *ids, float *w, int P, int E, int first,
-                       bool window, const PlanBuffers &plan, int nrt_gu, int nrt_dn, cudaStream_t st) {
+                       bool window, const PlanBuffers &plan, int nrt_gu, int nrt_dn, cudaStream_t st, int topk, int ids_ld,
+                       int w_ld) {
     RouteIngest in;
     in.src_ids = src_ids; in.src_w = src_w; in.dst_ids = ids; in.dst_w = w; in.first = first; in.window = window ? 1 : 0;
+    in.topk = topk; in.ids_ld = ids_ld; in.w_ld = w_ld;
     return launch_plan(ids, P, E, plan, nrt_gu, nrt_dn, in, st);
 }
 

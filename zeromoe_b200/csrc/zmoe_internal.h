@@ -136,7 +136,7 @@ int launch_router_prefill(const RouterArgs &a, cudaStream_t st);  // four launch
 // the planner, first copying routes from outside into the context's tables (ids, w); window: expert numbers
 // outside [first, first + E) become -1
 int launch_plan_ingest(const int32_t *src_ids, const float *src_w, int32_t *ids, float *w, int P, int E, int first,
-                       bool window, const PlanBuffers &plan, int nrt_gu, int nrt_dn, cudaStream_t st);
+                       bool window, const PlanBuffers &plan, int nrt_gu, int nrt_dn, cudaStream_t st, int topk = 0, int ids_ld = 0, int w_ld = 0);
 int launch_plan_from_ids(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
                          cudaStream_t st);
 int launch_plan_dense(int S, const PlanBuffers &plan, int nrt, cudaStream_t st);
