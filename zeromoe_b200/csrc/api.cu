@@ -243,15 +243,20 @@ int zmoe_layer_create(zmoe_ctx *ctx, const zmoe_layer_desc *desc, zmoe_layer **o
     L->ctx = ctx;
     L->d = d;
     L->dual = d.gate.type == d.up.type;
-    int rc = mmid_geometry(d.gate.type, d.d_model, d.d_ff, L->dual, &L->g_gu);
+    int rc = mmid_geometry(d.gate.type, d.d_model, d.d_ff, L->dual, &L->g_gu, true);
     if (!rc && !L->dual) {
-        rc = mmid_geometry(d.up.type, d.d_model, d.d_ff, false, &L->g_gate1);
+        rc = mmid_geometry(d.up.type, d.d_model, d.d_ff, false, &L->g_gate1, true);
+        // the two single projections share one item space: both on the K-chunked kernel (32-row items) or neither
+        if (!rc && L->g_gu.v2 != L->g_gate1.v2) {
+            rc = mmid_geometry(d.gate.type, d.d_model, d.d_ff, false, &L->g_gu, false);
+            if (!rc) rc = mmid_geometry(d.up.type, d.d_model, d.d_ff, false, &L->g_gate1, false);
+        }
         // both single projections share one item space: use the smaller tile for both
         if (!rc) {
             if (L->g_gate1.R < L->g_gu.R) L->g_gu.R = L->g_gate1.R; else L->g_gate1.R = L->g_gu.R;
         }
     }
-    if (!rc) rc = mmid_geometry(d.down.type, d.d_ff, d.d_model, false, &L->g_dn);
+    if (!rc) rc = mmid_geometry(d.down.type, d.d_ff, d.d_model, false, &L->g_dn, true);
     const zmoe_weight *ws[3] = {&d.gate, &d.up, &d.down};
     size_t *tot[3] = {&L->bytes_gate, &L->bytes_up, &L->bytes_down};
     for (int i = 0; i < 3 && !rc; ++i) {
@@ -271,13 +276,36 @@ int zmoe_layer_create(zmoe_ctx *ctx, const zmoe_layer_desc *desc, zmoe_layer **o
     L->nrt_dn = (d.d_model + L->g_dn.R - 1) / L->g_dn.R;
     {
         const int rb_gu = (d.d_model / QK_K) * block_bytes(d.gate.type), rb_dn = (d.d_ff / QK_K) * block_bytes(d.down.type);
-        if (L->dual && L->g_gu.rbs != rb_gu)
+        if (L->g_gu.v2) {
+            if (L->g_gu.tiled) {
+                L->has_tm_gu =
+                    make_chunk_map(&L->tm_gate, d.gate.data_dev, d.n_experts, d.d_ff, rb_gu, d.gate.expert_stride, L->g_gu.pitch) == ZMOE_OK;
+                if (L->dual)
+                    L->has_tm_gu = L->has_tm_gu && make_chunk_map(&L->tm_up, d.up.data_dev, d.n_experts, d.d_ff, rb_gu,
+                                                                  d.up.expert_stride, L->g_gu.pitch) == ZMOE_OK;
+                else if (L->g_gate1.tiled)
+                    L->has_tm_gu = L->has_tm_gu && make_chunk_map(&L->tm_up, d.up.data_dev, d.n_experts, d.d_ff,
+                                                                  (d.d_model / QK_K) * block_bytes(d.up.type), d.up.expert_stride,
+                                                                  L->g_gate1.pitch) == ZMOE_OK;
+                if (!L->has_tm_gu) rc = ZMOE_ERR_CUDA;
+            }
+        } else if (L->dual && L->g_gu.rbs != rb_gu)
             L->has_tm_gu =
                 make_rows_map(&L->tm_gate, d.gate.data_dev, d.n_experts, d.d_ff, rb_gu, d.gate.expert_stride, L->g_gu.R) == ZMOE_OK &&
                 make_rows_map(&L->tm_up, d.up.data_dev, d.n_experts, d.d_ff, rb_gu, d.up.expert_stride, L->g_gu.R) == ZMOE_OK;
-        if (L->g_dn.rbs != rb_dn)
+        if (L->g_dn.v2) {
+            if (L->g_dn.tiled) {
+                L->has_tm_dn = make_chunk_map(&L->tm_down, d.down.data_dev, d.n_experts, d.d_model, rb_dn, d.down.expert_stride,
+                                              L->g_dn.pitch) == ZMOE_OK;
+                if (!L->has_tm_dn) rc = ZMOE_ERR_CUDA;
+            }
+        } else if (L->g_dn.rbs != rb_dn)
             L->has_tm_dn = make_rows_map(&L->tm_down, d.down.data_dev, d.n_experts, d.d_model, rb_dn, d.down.expert_stride,
                                          L->g_dn.R) == ZMOE_OK;
+    }
+    if (rc) {
+        delete L;
+        return rc;
     }
     *out = L;
     return ZMOE_OK;
@@ -461,10 +489,13 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         m.I = d.d_model; m.O = d.d_ff; m.q8 = c->q8x; m.xdiv = d.topk; m.ldy = d.d_ff; m.down = false;
         m.type = d.up.type; m.w0 = d.up.data_dev; m.stride0 = d.up.expert_stride; m.total0 = L->bytes_up; m.y = ubuf;
         if (q8_layout_of(d.up.type) != q8_layout_of(d.gate.type)) m.q8 = c->q8x2;
+        m.tm0 = L->g_gate1.v2 && L->g_gate1.tiled ? &L->tm_up : nullptr;
         rc = launch_mmid(m, L->g_gate1, st);
         m.q8 = c->q8x;
         m.type = d.gate.type; m.w0 = d.gate.data_dev; m.stride0 = d.gate.expert_stride; m.total0 = L->bytes_gate; m.y = gbuf;
+        m.tm0 = L->g_gu.v2 && L->g_gu.tiled ? &L->tm_gate : nullptr;
         if (!rc) rc = launch_mmid(m, L->g_gu, st);
+        m.tm0 = nullptr;
         if (!rc) {
             launch_expert_swiglu(c->act, gbuf, ubuf, P * d.d_ff, d.swiglu_clamp, d.swiglu_clamp_fused, c->bad, stream);
             rc = ok(cudaPeekAtLastError());

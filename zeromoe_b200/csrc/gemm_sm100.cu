@@ -287,6 +287,20 @@ int make_rows_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t
     return r == CUDA_SUCCESS ? ZMOE_OK : ZMOE_ERR_CUDA;
 }
 
+int make_chunk_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t expert_stride, int pitch) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return ZMOE_ERR_CUDA;
+    if (rb % 16 || expert_stride % 16 || pitch % 16 || pitch / 8 > 256) return ZMOE_ERR_SHAPE;
+    const cuuint64_t dims[3] = {(cuuint64_t)(rb / 8), (cuuint64_t)O, (cuuint64_t)E};
+    const cuuint64_t strides[2] = {(cuuint64_t)rb, (cuuint64_t)expert_stride};
+    const cuuint32_t box[3] = {(cuuint32_t)(pitch / 8), 32, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void *>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? ZMOE_OK : ZMOE_ERR_CUDA;
+}
+
 int launch_gemm_sm100(const GemmLaunch &L, cudaStream_t st) {
     if (!gemm_sm100_supported(L.type, L.I, L.O)) return ZMOE_ERR_SHAPE;
     GemmFn fn = nullptr;

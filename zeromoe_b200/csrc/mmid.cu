@@ -4,14 +4,65 @@
 #include <utility>
 
 #include "mmid.cuh"
+#include "mmid2.cuh"
 #include "zmoe_internal.h"
 
 namespace zmoe {
 
-int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
+// Geometry of the K-chunked kernel, where one exists for the shape: chunks of cb super-blocks whose bytes are a
+// multiple of 16 (tiled copies; the tensor's rows must be multiples of 16 bytes too), or -- rows of at most eight
+// super-blocks -- the whole row as one chunk, copied as a contiguous run.
+static bool mmid2_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
+    const int bb = block_bytes(type), nb = I / QK_K, rb = nb * bb;
+    if (nb < 2 || rb % 4 != 0) return false;
+    const int ntile = dual ? 2 : 1;
+    const int budget = 200 * 1024;
+    int cands[5], nc = 0;
+    if (rb % 16 == 0) {
+        cands[nc++] = dual ? 4 : 8;
+        cands[nc++] = dual ? 8 : 4;
+        cands[nc++] = 2;
+    }
+    if (nb <= 8) cands[nc++] = nb;   // the whole row
+    for (int i = 0; i < nc; ++i) {
+        const int cb = cands[i];
+        if (cb > nb || nb % cb != 0) continue;
+        const bool whole = cb == nb;
+        const bool tiled = rb % 16 == 0 && (cb * bb) % 16 == 0;
+        if (!tiled && !whole) continue;
+        // a chunk that is not the whole row needs 16-byte pieces of the packed activation row as well: slices of
+        // four super-blocks (a slice then serves two chunks of two)
+        const int acb = whole ? cb : (cb == 2 ? 4 : cb);
+        if (!whole && (acb % 4 != 0 || nb % acb != 0)) continue;
+        int pitch = rb;
+        if (tiled) {
+            pitch = (cb * bb + 15) & ~15;
+            while ((pitch / 4) % 8 != 4) pitch += 16;   // fragment loads of eight rows fall into distinct banks
+            if (pitch / 8 > 256) continue;
+        }
+        const int I_l = acb * QK_K;
+        int q8s_l = q8row_stride(I_l);
+        while ((q8s_l / 4) % 16 == 0) q8s_l += 16;
+        const int wtile = (M2_R * pitch + 32 + 127) & ~127;
+        const int stage = (ntile * wtile + MMID_MAXTOK * q8s_l + 127) & ~127;
+        if ((size_t)stage * M2_NSET * M2_NSTG > (size_t)budget) continue;
+        g->v2 = 1; g->cb = cb; g->acb = acb; g->nch = nb / cb; g->pitch = pitch; g->tiled = tiled ? 1 : 0;
+        g->lb_log2 = cb * 4 > 16 ? 3 : 2;   // up to four units per lane
+        g->q8s_l = q8s_l;
+        g->R = M2_R; g->wtile_bytes = wtile; g->stage_bytes = stage; g->nstage = M2_NSTG;
+        g->smem_bytes = (size_t)stage * M2_NSET * M2_NSTG;
+        g->rbs = pitch; g->q8s = q8s_l; g->ncw = M2_NCW; g->lpr = 1 << g->lb_log2; g->upl = (cb * 4 + g->lpr - 1) / g->lpr;
+        return true;
+    }
+    return false;
+}
+
+int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g, bool allow_v2) {
     const int bb = block_bytes(type);
     if (bb == 0) return ZMOE_ERR_TYPE;
     if (I <= 0 || O <= 0 || I % QK_K != 0) return ZMOE_ERR_SHAPE;
+    *g = MmidGeom();
+    if (allow_v2 && mmid2_geometry(type, I, O, dual, g)) return ZMOE_OK;
     const int U = I / 64;
     if (U > 128) return ZMOE_ERR_SHAPE;  // rows longer than 8192 elements: no kernel yet
     if (U <= 32) {
@@ -109,7 +160,57 @@ static bool mma_split(int type, const MmidGeom &g, int I, bool dual, int *ks, in
     return true;
 }
 
+using Kernel2Fn = void (*)(const M2Params);
+
+template <bool DUAL>
+static Kernel2Fn pick2(int type, bool mma) {
+    switch (type) {
+    case Q2_K: return mma ? mmid2_kernel<Q2_K, DUAL, true> : mmid2_kernel<Q2_K, DUAL, false>;
+    case Q3_K: return mma ? mmid2_kernel<Q3_K, DUAL, true> : mmid2_kernel<Q3_K, DUAL, false>;
+    case Q4_K: return mma ? mmid2_kernel<Q4_K, DUAL, true> : mmid2_kernel<Q4_K, DUAL, false>;
+    case IQ2_XXS: return mmid2_kernel<IQ2_XXS, DUAL, false>;
+    }
+    return nullptr;
+}
+
+static int launch_mmid2(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
+    const bool mma = L.multi && (L.type == Q2_K || L.type == Q3_K || L.type == Q4_K);
+    Kernel2Fn fn = L.dual ? pick2<true>(L.type, mma) : pick2<false>(L.type, mma);
+    if (!fn) return ZMOE_ERR_TYPE;
+    if ((reinterpret_cast<size_t>(L.w0) & 15) || (L.dual && (reinterpret_cast<size_t>(L.w1) & 15))) return ZMOE_ERR_ALIGN;
+    if (g.tiled && (!L.tm0 || (L.dual && !L.tm1))) return ZMOE_ERR_ARG;
+    if (raise_dynamic_smem(reinterpret_cast<const void *>(fn), 200 * 1024) != ZMOE_OK) return ZMOE_ERR_CUDA;
+    M2Params p;
+    p.w0 = static_cast<const uint8_t *>(L.w0);
+    p.w1 = static_cast<const uint8_t *>(L.w1);
+    p.stride0 = L.stride0; p.stride1 = L.stride1;
+    p.total0 = L.total0; p.total1 = L.total1;
+    p.I = L.I; p.O = L.O;
+    p.rb = (L.I / QK_K) * block_bytes(L.type);
+    p.cb = g.cb; p.nch = g.nch; p.cbytes = g.cb * block_bytes(L.type);
+    p.acb = g.acb;
+    p.pitch = g.pitch; p.lb_log2 = g.lb_log2; p.I_l = g.acb * QK_K; p.q8s_l = g.q8s_l; p.tiled = g.tiled;
+    if (g.tiled) {
+        p.tm0 = *L.tm0;
+        if (L.dual) p.tm1 = *L.tm1;
+    }
+    p.q8 = L.q8;
+    p.q8_stride = q8row_stride(L.I);
+    p.xdiv = L.xdiv;
+    p.y = L.y; p.ldy = L.ldy;
+    p.plan.hdr = L.plan.hdr; p.plan.active = L.plan.active; p.plan.offs = L.plan.offs; p.plan.slot = L.plan.slot;
+    p.plan.item_offs = L.down ? L.plan.item_offs_dn : L.plan.item_offs_gu;
+    p.plan.aoffs = L.plan.aoffs; p.plan.antok = L.plan.antok; p.plan.cap_e = L.plan.cap_e;
+    p.hdr_items = L.down ? 2 : 1;
+    p.clamp = L.clamp; p.clamp_fused = L.clamp_fused;
+    p.stage_bytes = g.stage_bytes; p.wtile_bytes = g.wtile_bytes;
+    p.err = L.err;
+    p.bad = L.dual ? L.bad : nullptr;
+    return launch_pdl(fn, dim3(L.n_sm), dim3(32 * (M2_NCW + 1)), g.smem_bytes, st, p) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+}
+
 int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
+    if (g.v2) return launch_mmid2(L, g, st);
     int mma_ks = 0, mma_hpw = 0;
     const bool mma = L.multi && mma_split(L.type, g, L.I, L.dual, &mma_ks, &mma_hpw);
     KernelFn fn = L.dual ? pick_type<true>(L.type, g.lpr, g.upl, mma) : pick_type<false>(L.type, g.lpr, g.upl, mma);

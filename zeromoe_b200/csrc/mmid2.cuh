@@ -1,0 +1,417 @@
+// mmid2.cuh -- the decode-shaped MUL_MAT_ID kernel with K-chunked stages and independent warp sets.
+//
+// Same job and same arithmetic as mmid.cuh (quantised expert rows against Q8_K activations, one persistent
+// CTA per SM, replaces reference core/gpu_expert_executor.cpp:358-387,512-513 and
+// kernels/quant/kquant_matmul.cu:647-700), restructured around what limited that kernel: every consumer warp
+// paid the fixed cost of a pipeline stage (barrier wait, descriptor, activation reload, reduction) for one or
+// two rows' worth of work.
+//   * An item is (expert, 32 consecutive rows, <= MMID_MAXTOK pairs).  It is streamed as chunks of CB
+//     super-blocks of all 32 rows: a stage holds [32 rows x CB blocks] of the tile (two tiles in DUAL mode)
+//     and the matching slice of the pairs' packed activation rows.  Where the tensor's rows are multiples of
+//     16 bytes the chunk is one tiled copy (box = chunk width x 32 rows); short rows of any length that is a
+//     multiple of 4 bytes are copied whole (one chunk) as a contiguous run.
+//   * The 12 consumer warps form three sets of four.  Each set has its own ring of two stages and works on
+//     its own item: a warp's share of a stage is 8 rows x CB blocks (x 2 matrices), accumulated in registers
+//     across the item's chunks, so the per-stage fixed cost is spread over 8 to 16 times more arithmetic and no
+//     reduction runs until the item ends.  The producer warp hands the next item to whichever set is free.
+//   * One pair per item: a lane owns one super-block of one row (and of its partner row in the other matrix).
+//     Two or more pairs: mma.sync on 16-row pieces (mmid_mma.cuh); the set's warps split pieces and matrices
+//     (DUAL) or pieces and halves of the chunk, and meet through shared memory once per item.
+// Every wait is bounded; on expiry the warp raises the error flag and leaves.
+#pragma once
+
+#include "mmid.cuh"
+
+namespace zmoe {
+
+constexpr int M2_NSET = 3;             // independent warp sets
+constexpr int M2_WPS = 4;              // warps per set
+constexpr int M2_NSTG = 2;             // stages per set
+constexpr int M2_NCW = M2_NSET * M2_WPS;
+constexpr int M2_R = 32;               // rows per item
+
+struct M2Params {
+    const uint8_t *w0, *w1;
+    size_t stride0, stride1, total0, total1;
+    int I, O, rb;
+    int cb;          // super-blocks per chunk
+    int nch;         // chunks per row
+    int cbytes;      // bytes of one row's chunk in global memory
+    int pitch;       // bytes between rows of a tile in shared memory
+    int lb_log2;     // one-pair path: log2 of the lanes that share a row (one super-block each)
+    int acb;         // super-blocks of the activation slice a stage holds: cb, or 4 where cb is 2 (a slice
+                     // must be copyable in 16-byte pieces; the slice then serves two consecutive chunks)
+    int I_l;         // elements of that slice
+    int q8s_l;       // bytes between the pairs' activation slices in shared memory
+    int tiled;       // chunks come through tm0 / tm1
+    const uint8_t *q8;
+    int q8_stride, xdiv;
+    float *y;
+    int ldy;
+    PlanView plan;
+    int hdr_items;
+    float clamp;
+    int clamp_fused;
+    int stage_bytes, wtile_bytes;
+    int *err, *bad;
+    alignas(64) CUtensorMap tm0, tm1;
+};
+
+struct M2Meta {
+    int expert, r0, nrows, ntok;
+    int chunk, flags;          // flags: 1 = last chunk of the item, 2 = no more items for this set
+    int w0_off, w1_off;
+    int pair[MMID_MAXTOK];
+    int pad[4];
+};
+static_assert(sizeof(M2Meta) == 64, "meta");
+
+// 3-D tiled copy (no multicast): box of the map at (x, row, expert)
+__device__ __forceinline__ void tma_load_chunk(void *dst_smem, const void *tmap, int x, int row, int expert, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(dst_smem)), "l"(tmap), "r"(x), "r"(row), "r"(expert), "r"(smem_u32(bar))
+        : "memory");
+}
+
+template <int TYPE, bool DUAL, bool MMA>
+__global__ void __launch_bounds__(32 * (M2_NCW + 1), 1) mmid2_kernel(const __grid_constant__ M2Params p) {
+    constexpr int BB = QTraits<TYPE>::kBytes;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[M2_NSET][M2_NSTG], empty_bar[M2_NSET][M2_NSTG], x_bar[M2_NSET][2];
+    __shared__ M2Meta meta[M2_NSET][M2_NSTG];
+    __shared__ __align__(16) float exch[MMA ? M2_NSET : 1][2][2][32][4];   // [set][item parity][piece][lane]
+    __shared__ __align__(8) uint64_t iq2_grid[TYPE == IQ2_XXS ? 256 : 1], iq2_sign[TYPE == IQ2_XXS ? 128 : 1];
+    __shared__ int s_item_offs[MMID_PLAN_SMEM + 1], s_active[MMID_PLAN_SMEM], s_aoffs[MMID_PLAN_SMEM],
+        s_antok[MMID_PLAN_SMEM];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < M2_NSET; ++s) {
+            for (int g = 0; g < M2_NSTG; ++g) {
+                mbar_init(&full_bar[s][g], 1);
+                mbar_init(&empty_bar[s][g], M2_WPS);
+            }
+            mbar_init(&x_bar[s][0], 2);
+            mbar_init(&x_bar[s][1], 2);
+        }
+        mbar_init_fence();
+    }
+    if (TYPE == IQ2_XXS) iq2_fill_tables(iq2_grid, iq2_sign);
+    __syncthreads();
+
+    // everything below reads what earlier kernels of the stream wrote
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+
+    const int n_items = p.plan.hdr[p.hdr_items];
+    const int n_active = p.plan.hdr[0];
+    for (int i = tid; i < MMID_PLAN_SMEM && i < p.plan.cap_e; i += blockDim.x) {
+        s_item_offs[i + 1] = p.plan.item_offs[i + 1];
+        s_active[i] = p.plan.active[i];
+        s_aoffs[i] = p.plan.aoffs[i];
+        s_antok[i] = p.plan.antok[i];
+    }
+    if (tid == 0) s_item_offs[0] = 0;
+    __syncthreads();
+    const bool plan_in_smem = n_active <= MMID_PLAN_SMEM;
+    const int G = (int)gridDim.x;
+    const int n_mine = n_items > (int)blockIdx.x ? (n_items - (int)blockIdx.x + G - 1) / G : 0;
+    const int nrt = (p.O + M2_R - 1) / M2_R;
+
+    if (warp == M2_NCW) {
+        // ------------------------------ producer ------------------------------
+        // Items of this CTA (dealt round-robin over the grid) are resolved 32 at a time, one per lane; a set
+        // that needs work takes the next one, so sets with light items simply take more of them.
+        int next = 0, batch_base = -64;
+        int e = 0, r0 = 0, nrows = 0, ntok = 0, pr[MMID_MAXTOK];
+#pragma unroll
+        for (int t = 0; t < MMID_MAXTOK; ++t) pr[t] = 0;
+        int s_e[M2_NSET], s_r0[M2_NSET], s_nrows[M2_NSET], s_ntok[M2_NSET], s_pair[M2_NSET], s_c[M2_NSET], s_f[M2_NSET],
+            s_state[M2_NSET];   // 0: needs an item, 1: issuing an item's chunks, 2: finished
+#pragma unroll
+        for (int s = 0; s < M2_NSET; ++s) { s_e[s] = s_r0[s] = s_nrows[s] = s_ntok[s] = s_pair[s] = s_c[s] = s_f[s] = s_state[s] = 0; }
+        const uint32_t act_bytes = p.nch == 1 ? (uint32_t)p.q8_stride
+                                              : (uint32_t)(p.acb * 4 * Q8_UNIT_STRIDE + ((p.acb * 4 + 15) & ~15) + p.acb * 32);
+        const int cpa = p.acb / p.cb;   // chunks per activation slice
+        int idle = 0;
+        for (;;) {
+            bool progress = false, all_done = true;
+#pragma unroll
+            for (int s = 0; s < M2_NSET; ++s) {
+                if (s_state[s] == 2) continue;
+                all_done = false;
+                if (s_state[s] == 0 && next < n_mine) {
+                    if (next >= batch_base + 32) {
+                        batch_base = next;
+                        const int mine = (int)blockIdx.x + (batch_base + lane) * G;
+                        if (batch_base + lane < n_mine) {
+                            int lo = 0, hi = n_active - 1;   // last a with item_offs[a] <= mine
+                            int local, ebase, ecnt;
+                            if (plan_in_smem) {
+                                while (lo < hi) {
+                                    const int mid = (lo + hi + 1) >> 1;
+                                    if (s_item_offs[mid] <= mine) lo = mid; else hi = mid - 1;
+                                }
+                                e = s_active[lo]; local = mine - s_item_offs[lo]; ebase = s_aoffs[lo]; ecnt = s_antok[lo];
+                            } else {
+                                while (lo < hi) {
+                                    const int mid = (lo + hi + 1) >> 1;
+                                    if (p.plan.item_offs[mid] <= mine) lo = mid; else hi = mid - 1;
+                                }
+                                e = p.plan.active[lo]; local = mine - p.plan.item_offs[lo];
+                                ebase = p.plan.aoffs[lo]; ecnt = p.plan.antok[lo];
+                            }
+                            const int tc = local / nrt, rt = local % nrt;
+                            r0 = rt * M2_R;
+                            nrows = min(M2_R, p.O - r0);
+                            const int s0 = ebase + tc * MMID_MAXTOK;
+                            ntok = min(MMID_MAXTOK, ecnt - tc * MMID_MAXTOK);
+#pragma unroll
+                            for (int t = 0; t < MMID_MAXTOK; ++t)
+                                if (t < ntok) pr[t] = p.plan.slot[s0 + t];
+                        }
+                    }
+                    const int j = next - batch_base;
+                    s_e[s] = __shfl_sync(0xffffffffu, e, j);
+                    s_r0[s] = __shfl_sync(0xffffffffu, r0, j);
+                    s_nrows[s] = __shfl_sync(0xffffffffu, nrows, j);
+                    s_ntok[s] = __shfl_sync(0xffffffffu, ntok, j);
+#pragma unroll
+                    for (int t = 0; t < MMID_MAXTOK; ++t) {
+                        const int v = __shfl_sync(0xffffffffu, pr[t], j);
+                        if (lane == t) s_pair[s] = v;
+                    }
+                    s_c[s] = 0;
+                    s_state[s] = 1;
+                    ++next;
+                }
+                // is the set's next stage free?  One lane polls, so that the warp cannot split on the answer.
+                const int slot = s_f[s] % M2_NSTG;
+                int is_free = 1;
+                if (s_f[s] >= M2_NSTG) {
+                    if (lane == 0) is_free = mbar_try_wait(&empty_bar[s][slot], ((s_f[s] / M2_NSTG) - 1) & 1) ? 1 : 0;
+                    is_free = __shfl_sync(0xffffffffu, is_free, 0);
+                }
+                if (!is_free) continue;
+                progress = true;
+                M2Meta &m = meta[s][slot];
+                if (s_state[s] == 0) {
+                    // nothing left: tell the set to stop
+                    if (lane == 0) {
+                        m.flags = 2;
+                        mbar_arrive(&full_bar[s][slot]);
+                    }
+                    s_state[s] = 2;
+                    ++s_f[s];
+                    continue;
+                }
+                const int c = s_c[s];
+                uint8_t *stage = smem + (size_t)(s * M2_NSTG + slot) * p.stage_bytes;
+                uint8_t *q8dst = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
+                uint32_t bytes = 0;
+                if (lane == 0) {
+                    m.expert = s_e[s]; m.r0 = s_r0[s]; m.nrows = s_nrows[s]; m.ntok = s_ntok[s];
+                    m.chunk = c; m.flags = c + 1 == p.nch ? 1 : 0;
+                    m.w0_off = 0; m.w1_off = 0;
+                    if (p.tiled) {
+                        // the box is always 32 full rows of `pitch` bytes: rows past the expert's last and bytes past
+                        // the row's end arrive as zeros
+                        const int x = (c * p.cbytes) >> 3;   // the maps count in 8-byte elements
+                        tma_load_chunk(stage, &p.tm0, x, s_r0[s], s_e[s], &full_bar[s][slot]);
+                        if (DUAL) tma_load_chunk(stage + p.wtile_bytes, &p.tm1, x, s_r0[s], s_e[s], &full_bar[s][slot]);
+                        bytes = (uint32_t)(M2_R * p.pitch) * (DUAL ? 2u : 1u);
+                    } else {
+                        const size_t g0 = (size_t)s_e[s] * p.stride0 + (size_t)s_r0[s] * p.rb;
+                        bytes += issue_tile(stage, p.w0, p.total0, g0, g0 + (size_t)s_nrows[s] * p.rb, &full_bar[s][slot], &m.w0_off);
+                        if (DUAL) {
+                            const size_t h0 = (size_t)s_e[s] * p.stride1 + (size_t)s_r0[s] * p.rb;
+                            bytes += issue_tile(stage + p.wtile_bytes, p.w1, p.total1, h0, h0 + (size_t)s_nrows[s] * p.rb,
+                                                &full_bar[s][slot], &m.w1_off);
+                        }
+                    }
+                }
+                if (lane < s_ntok[s]) {
+                    // this chunk's slice of the pair's packed activation row, laid out as a row of I_l elements
+                    const int my_pair = s_pair[s];
+                    m.pair[lane] = my_pair;
+                    const uint8_t *src = p.q8 + (size_t)(my_pair / p.xdiv) * p.q8_stride;
+                    uint8_t *dst = q8dst + (size_t)lane * p.q8s_l;
+                    if (p.nch == 1) {
+                        bulk_g2s(dst, src, (uint32_t)p.q8_stride, &full_bar[s][slot]);
+                    } else {
+                        const uint32_t ub = (uint32_t)(p.acb * 4 * Q8_UNIT_STRIDE), db = (uint32_t)((p.acb * 4 + 15) & ~15),
+                                       sb = (uint32_t)(p.acb * 32);
+                        const int ca = c / cpa;
+                        bulk_g2s(dst, src + (size_t)ca * ub, ub, &full_bar[s][slot]);
+                        bulk_g2s(dst + q8row_d_off(p.I_l), src + q8row_d_off(p.I) + ca * p.acb * 4, db, &full_bar[s][slot]);
+                        bulk_g2s(dst + q8row_bs_off(p.I_l), src + q8row_bs_off(p.I) + ca * p.acb * 32, sb, &full_bar[s][slot]);
+                    }
+                }
+                __syncwarp();
+                // the producer's own arrival, with the byte count, is what lets the phase complete
+                if (lane == 0) mbar_arrive_expect_tx(&full_bar[s][slot], bytes + (uint32_t)s_ntok[s] * act_bytes);
+                ++s_f[s];
+                if (++s_c[s] == p.nch) s_state[s] = 0;
+            }
+            if (all_done) break;
+            if (progress) {
+                idle = 0;
+            } else {
+                if (++idle > (1 << 20)) {
+                    if (lane == 0) atomicExch(p.err, 1);
+                    break;
+                }
+                __nanosleep(40);
+            }
+        }
+    } else {
+        // ------------------------------ consumers -----------------------------
+        const int set = warp / M2_WPS, ws = warp % M2_WPS;
+        Iq2Tables tb;
+        tb.grid = smem_u32(iq2_grid);
+        tb.signs = smem_u32(iq2_sign);
+        // one-pair path: lane = (row rl of the warp's rows, run bl of upl consecutive 64-element units of the chunk)
+        const int LB = 1 << p.lb_log2, bl = lane & (LB - 1), rl = lane >> p.lb_log2, rpp = 32 >> p.lb_log2;
+        const int np = M2_R / (M2_WPS * rpp);   // passes over the tile: 1 (four lanes per row) or 2 (eight)
+        const int n_units = 4 * p.cb, upl = (n_units + LB - 1) >> p.lb_log2;
+        const int cpa = p.acb / p.cb;
+        float acc[2][2][MMID_MAXTOK];           // [pass][matrix][pair]
+        float f0[4] = {0.f, 0.f, 0.f, 0.f};     // tensor-core path: (row g | g+8) x (pair 2c | 2c+1)
+        // tensor-core path: warp = (16-row piece, matrix) in DUAL mode, (piece, half of the chunk) otherwise
+        const int piece = ws >> 1, half = ws & 1;
+        int hb0 = 0, hb1 = 2 * p.cb;
+        if (!DUAL) {
+            int mid = p.cb;                                          // in half super-blocks
+            if (MmaPath<TYPE>::kGrain == 2) mid = (mid + 1) & ~1;
+            if (half == 0) hb1 = mid; else hb0 = mid;
+        }
+        int fcount = 0, n_mma = 0;
+        for (;;) {
+            const int slot = fcount % M2_NSTG;
+            if (!mbar_wait(&full_bar[set][slot], (fcount / M2_NSTG) & 1)) {
+                if (lane == 0) atomicExch(p.err, 2);
+                break;
+            }
+            const M2Meta &m = meta[set][slot];
+            const int flags = m.flags;
+            if (flags & 2) break;
+            const int m_nrows = m.nrows, m_ntok = m.ntok, m_r0 = m.r0;
+            const uint32_t stage = smem_u32(smem + (size_t)(set * M2_NSTG + slot) * p.stage_bytes);
+            const uint32_t t0 = stage + m.w0_off;
+            const uint32_t t1 = stage + p.wtile_bytes + m.w1_off;
+            const uint32_t q8base = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
+            const bool mma_item = MMA && m_ntok >= 2;
+            const int ab = (m.chunk % cpa) * p.cb;   // where the chunk's blocks sit inside the activation slice
+            if (m.chunk == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) f0[i] = 0.f;
+#pragma unroll
+                for (int a = 0; a < 2; ++a)
+#pragma unroll
+                    for (int b = 0; b < 2; ++b)
+#pragma unroll
+                        for (int t = 0; t < MMID_MAXTOK; ++t) acc[a][b][t] = 0.f;
+            }
+            if (mma_item) {
+                // block b of the activation slice meets block b - ab of the chunk: shift the tile instead of the index
+                if (piece * 16 < m_nrows && hb0 < hb1)
+                    mma_rows<TYPE, false>((DUAL && half ? t1 : t0) + (uint32_t)(piece * 16) * p.pitch - (uint32_t)(ab * BB), 0, p.pitch,
+                                          q8base, p.q8s_l, p.I_l, hb0 + 2 * ab, hb1 + 2 * ab, lane, f0, f0);
+            } else {
+#pragma unroll
+                for (int tk = 0; tk < MMID_MAXTOK; ++tk) {
+                    if (tk < m_ntok) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int u = bl * upl + i;
+                            if (i >= upl || u >= n_units) continue;
+                            const int sub = u & 3;
+                            const uint32_t boff = (uint32_t)(u >> 2) * BB;
+                            UnitAct ua;
+                            load_unit_act<TYPE>(q8base + tk * p.q8s_l, p.I_l, 4 * ab + u, ua);
+#pragma unroll
+                            for (int pp = 0; pp < 2; ++pp) {
+                                if (pp < np) {
+                                    const uint32_t roff = (uint32_t)(pp * M2_WPS * rpp + ws * rpp + rl) * p.pitch + boff;
+                                    int is, ms;
+                                    float d, dm;
+                                    unit_dot<TYPE>(t0 + roff, sub, ua, tb, is, ms, d, dm);
+                                    acc[pp][0][tk] = fmaf(d * ua.d, (float)is, acc[pp][0][tk]);
+                                    if (QTraits<TYPE>::kHasMin) acc[pp][0][tk] = fmaf(-(dm * ua.d), (float)ms, acc[pp][0][tk]);
+                                    if (DUAL) {
+                                        unit_dot<TYPE>(t1 + roff, sub, ua, tb, is, ms, d, dm);
+                                        acc[pp][1][tk] = fmaf(d * ua.d, (float)is, acc[pp][1][tk]);
+                                        if (QTraits<TYPE>::kHasMin) acc[pp][1][tk] = fmaf(-(dm * ua.d), (float)ms, acc[pp][1][tk]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if (flags & 1) {
+                // ---- the item is complete: reduce, activate, store (before the stage is released, which orders
+                // this item's use of the exchange buffer before the use two items later) ----
+                if (mma_item) {
+                    const int par = n_mma & 1;
+                    float *mine = &exch[MMA ? set : 0][par][piece][lane][0];
+                    if (half == 1) {
+                        *reinterpret_cast<float4 *>(mine) = make_float4(f0[0], f0[1], f0[2], f0[3]);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&x_bar[set][par]);
+                    } else {
+                        if (!mbar_wait(&x_bar[set][par], (n_mma >> 1) & 1)) {
+                            if (lane == 0) atomicExch(p.err, 3);
+                            break;
+                        }
+                        const float4 o = *reinterpret_cast<const float4 *>(mine);
+                        const float other[4] = {o.x, o.y, o.z, o.w};
+                        const int g = lane >> 2, c = lane & 3;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int row = piece * 16 + g + (i >> 1) * 8, tk = 2 * c + (i & 1);
+                            if (tk < m_ntok && row < m_nrows) {
+                                float v;
+                                if (DUAL) {
+                                    count_bad(p.bad, f0[i], other[i]);
+                                    v = swiglu_f(f0[i], other[i], p.clamp, p.clamp_fused);
+                                } else {
+                                    v = f0[i] + other[i];
+                                }
+                                p.y[(size_t)m.pair[tk] * p.ldy + m_r0 + row] = v;
+                            }
+                        }
+                    }
+                    ++n_mma;
+                } else {
+#pragma unroll
+                    for (int pp = 0; pp < 2; ++pp) {
+                        if (pp < np) {
+                            const int row = pp * M2_WPS * rpp + ws * rpp + rl;
+#pragma unroll
+                            for (int tk = 0; tk < MMID_MAXTOK; ++tk) {
+                                if (tk < m_ntok) {
+                                    float a0 = acc[pp][0][tk], a1 = DUAL ? acc[pp][1][tk] : 0.f;
+                                    for (int off = LB >> 1; off > 0; off >>= 1) {
+                                        a0 += __shfl_xor_sync(0xffffffffu, a0, off);
+                                        if (DUAL) a1 += __shfl_xor_sync(0xffffffffu, a1, off);
+                                    }
+                                    if (TYPE == IQ2_XXS) { a0 *= 0.125f; a1 *= 0.125f; }
+                                    if (bl == 0 && row < m_nrows) {
+                                        if (DUAL) count_bad(p.bad, a0, a1);
+                                        p.y[(size_t)m.pair[tk] * p.ldy + m_r0 + row] = DUAL ? swiglu_f(a0, a1, p.clamp, p.clamp_fused) : a0;
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[set][slot]);
+            ++fcount;
+        }
+    }
+}
+
+}  // namespace zmoe

@@ -71,8 +71,20 @@ struct MmidGeom {
     int nstage, stage_bytes, wtile_bytes;
     int rbs, q8s;          // shared-memory strides of weight rows and of activation rows
     size_t smem_bytes;
+    // K-chunked kernel (mmid2.cuh), chosen where the shape allows it and the caller can supply its maps
+    int v2 = 0;            // 1: launch_mmid takes the K-chunked kernel; R is then 32
+    int cb = 0, nch = 0;   // super-blocks per chunk, chunks per row
+    int acb = 0;           // super-blocks of the activation slice a stage holds (cb, or 4 where cb is 2)
+    int pitch = 0;         // bytes between rows of a chunk in shared memory
+    int lb_log2 = 0;       // log2 of the lanes that share a row on the one-pair path
+    int q8s_l = 0;         // bytes between the pairs' activation slices in shared memory
+    int tiled = 0;         // chunks come through tiled maps (make_chunk_map); 0: rows are copied whole as one run
 };
-int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g);
+// allow_v2: the caller passes maps made by make_chunk_map where g->tiled is set
+int mmid_geometry(int type, int I, int O, bool dual, MmidGeom *g, bool allow_v2 = false);
+// Map of a [E][O rows][rb bytes] weight tensor whose box is 32 rows of `pitch` bytes starting at any multiple of 16
+// bytes inside a row: bytes past the end of a row and rows past the last arrive as zeros.
+int make_chunk_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t expert_stride, int pitch);
 
 struct MmidLaunch {
     int type;
