@@ -54,8 +54,20 @@ struct M2Params {
     int clamp_fused;
     int stage_bytes, wtile_bytes;
     int *err, *bad;
+    unsigned long long *stats;   // cycle counters (builds with ZMOE_GEMM_STATS only), or null
     alignas(64) CUtensorMap tm0, tm1;
 };
+
+// Cycle accounting, compiled in with -DZMOE_GEMM_STATS: every warp adds its clock64() differences to
+//   [0] consumers waiting for a stage  [1] consumers working  [2] producer with nothing to issue
+//   [3] producer issuing  [4] stages filled  [5] stages consumed (per warp)
+#ifdef ZMOE_GEMM_STATS
+#define M2STAT_NOW() clock64()
+#define M2STAT_ADD(slot, v) do { if (p.stats && lane == 0) atomicAdd(&p.stats[slot], (unsigned long long)(v)); } while (0)
+#else
+#define M2STAT_NOW() 0ll
+#define M2STAT_ADD(slot, v) do { } while (0)
+#endif
 
 struct M2Meta {
     int expert, r0, nrows, ntok;
@@ -75,7 +87,7 @@ __device__ __forceinline__ void tma_load_chunk(void *dst_smem, const void *tmap,
 }
 
 template <int TYPE, bool DUAL, bool MMA>
-__global__ void __launch_bounds__(32 * (M2_NCW + 1), 1) mmid2_kernel(const __grid_constant__ M2Params p) {
+__global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __grid_constant__ M2Params p) {
     constexpr int BB = QTraits<TYPE>::kBytes;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[M2_NSET][M2_NSTG], empty_bar[M2_NSET][M2_NSTG], x_bar[M2_NSET][2];
@@ -84,8 +96,10 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 1), 1) mmid2_kernel(const __gri
     __shared__ __align__(8) uint64_t iq2_grid[TYPE == IQ2_XXS ? 256 : 1], iq2_sign[TYPE == IQ2_XXS ? 128 : 1];
     __shared__ int s_item_offs[MMID_PLAN_SMEM + 1], s_active[MMID_PLAN_SMEM], s_aoffs[MMID_PLAN_SMEM],
         s_antok[MMID_PLAN_SMEM];
+    __shared__ int s_next;   // the CTA's next item
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
+        s_next = 0;
         for (int s = 0; s < M2_NSET; ++s) {
             for (int g = 0; g < M2_NSTG; ++g) {
                 mbar_init(&full_bar[s][g], 1);
@@ -118,123 +132,97 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 1), 1) mmid2_kernel(const __gri
     const int n_mine = n_items > (int)blockIdx.x ? (n_items - (int)blockIdx.x + G - 1) / G : 0;
     const int nrt = (p.O + M2_R - 1) / M2_R;
 
-    if (warp == M2_NCW) {
-        // ------------------------------ producer ------------------------------
-        // Items of this CTA (dealt round-robin over the grid) are resolved 32 at a time, one per lane; a set
-        // that needs work takes the next one, so sets with light items simply take more of them.
-        int next = 0, batch_base = -64;
-        int e = 0, r0 = 0, nrows = 0, ntok = 0, pr[MMID_MAXTOK];
-#pragma unroll
-        for (int t = 0; t < MMID_MAXTOK; ++t) pr[t] = 0;
-        int s_e[M2_NSET], s_r0[M2_NSET], s_nrows[M2_NSET], s_ntok[M2_NSET], s_pair[M2_NSET], s_c[M2_NSET], s_f[M2_NSET],
-            s_state[M2_NSET];   // 0: needs an item, 1: issuing an item's chunks, 2: finished
-#pragma unroll
-        for (int s = 0; s < M2_NSET; ++s) { s_e[s] = s_r0[s] = s_nrows[s] = s_ntok[s] = s_pair[s] = s_c[s] = s_f[s] = s_state[s] = 0; }
+    if (warp >= M2_NCW) {
+        // ------------------------------ producers -----------------------------
+        // One warp per set (a spare warp rounds the CTA to 16 and leaves at once).  A producer takes the CTA's
+        // next item from a shared counter -- sets with light items simply take more of them -- resolves it
+        // while the previous item's chunks are still being issued, and feeds its set's two stages.
+        const int s = warp - M2_NCW;
+        if (s >= M2_NSET) return;
         const uint32_t act_bytes = p.nch == 1 ? (uint32_t)p.q8_stride
                                               : (uint32_t)(p.acb * 4 * Q8_UNIT_STRIDE + ((p.acb * 4 + 15) & ~15) + p.acb * 32);
-        const int cpa = p.acb / p.cb;   // chunks per activation slice
-        int idle = 0;
-        for (;;) {
-            bool progress = false, all_done = true;
-#pragma unroll
-            for (int s = 0; s < M2_NSET; ++s) {
-                if (s_state[s] == 2) continue;
-                all_done = false;
-                if (s_state[s] == 0 && next < n_mine) {
-                    if (next >= batch_base + 32) {
-                        batch_base = next;
-                        const int mine = (int)blockIdx.x + (batch_base + lane) * G;
-                        if (batch_base + lane < n_mine) {
-                            int lo = 0, hi = n_active - 1;   // last a with item_offs[a] <= mine
-                            int local, ebase, ecnt;
-                            if (plan_in_smem) {
-                                while (lo < hi) {
-                                    const int mid = (lo + hi + 1) >> 1;
-                                    if (s_item_offs[mid] <= mine) lo = mid; else hi = mid - 1;
-                                }
-                                e = s_active[lo]; local = mine - s_item_offs[lo]; ebase = s_aoffs[lo]; ecnt = s_antok[lo];
-                            } else {
-                                while (lo < hi) {
-                                    const int mid = (lo + hi + 1) >> 1;
-                                    if (p.plan.item_offs[mid] <= mine) lo = mid; else hi = mid - 1;
-                                }
-                                e = p.plan.active[lo]; local = mine - p.plan.item_offs[lo];
-                                ebase = p.plan.aoffs[lo]; ecnt = p.plan.antok[lo];
-                            }
-                            const int tc = local / nrt, rt = local % nrt;
-                            r0 = rt * M2_R;
-                            nrows = min(M2_R, p.O - r0);
-                            const int s0 = ebase + tc * MMID_MAXTOK;
-                            ntok = min(MMID_MAXTOK, ecnt - tc * MMID_MAXTOK);
-#pragma unroll
-                            for (int t = 0; t < MMID_MAXTOK; ++t)
-                                if (t < ntok) pr[t] = p.plan.slot[s0 + t];
-                        }
-                    }
-                    const int j = next - batch_base;
-                    s_e[s] = __shfl_sync(0xffffffffu, e, j);
-                    s_r0[s] = __shfl_sync(0xffffffffu, r0, j);
-                    s_nrows[s] = __shfl_sync(0xffffffffu, nrows, j);
-                    s_ntok[s] = __shfl_sync(0xffffffffu, ntok, j);
-#pragma unroll
-                    for (int t = 0; t < MMID_MAXTOK; ++t) {
-                        const int v = __shfl_sync(0xffffffffu, pr[t], j);
-                        if (lane == t) s_pair[s] = v;
-                    }
-                    s_c[s] = 0;
-                    s_state[s] = 1;
-                    ++next;
+        const int cpa = p.acb / p.cb;
+        long long st_idle = 0, st_busy = 0, st_fills = 0;
+        // item descriptor: e, r0, nrows, ntok and, in lane t < ntok, pair t
+        struct Item { int e, r0, nrows, ntok, pair; };
+        auto take = [&](Item &it) -> bool {
+            int j = 0;
+            if (lane == 0) j = atomicAdd(&s_next, 1);
+            j = __shfl_sync(0xffffffffu, j, 0);
+            if (j >= n_mine) return false;
+            const int mine = (int)blockIdx.x + j * G;   // items are dealt round-robin over the grid
+            // last a with item_offs[a] <= mine: the lanes probe 32 points of the range at once
+            int lo = 0, hi = n_active - 1;
+            while (lo < hi) {
+                const int span = hi - lo, step = (span + 31) >> 5;
+                const int probe = min(hi, lo + (lane + 1) * step);
+                const int v = plan_in_smem ? s_item_offs[probe] : p.plan.item_offs[probe];
+                const unsigned le = __ballot_sync(0xffffffffu, v <= mine);
+                // probes are increasing: the lanes that satisfy the test form a prefix
+                const int k = __popc(le);
+                const int nlo = k == 0 ? lo : min(hi, lo + k * step);
+                const int nhi = k == 32 ? hi : min(hi, lo + (k + 1) * step) - 1;
+                lo = nlo;
+                hi = max(nlo, nhi);
+            }
+            int e, local, ebase, ecnt;
+            if (plan_in_smem) {
+                e = s_active[lo]; local = mine - s_item_offs[lo]; ebase = s_aoffs[lo]; ecnt = s_antok[lo];
+            } else {
+                e = p.plan.active[lo]; local = mine - p.plan.item_offs[lo]; ebase = p.plan.aoffs[lo]; ecnt = p.plan.antok[lo];
+            }
+            const int tc = local / nrt, rt = local % nrt;
+            it.e = e;
+            it.r0 = rt * M2_R;
+            it.nrows = min(M2_R, p.O - it.r0);
+            it.ntok = min(MMID_MAXTOK, ecnt - tc * MMID_MAXTOK);
+            it.pair = lane < it.ntok ? p.plan.slot[ebase + tc * MMID_MAXTOK + lane] : 0;
+            return true;
+        };
+        Item cur, nxt;
+        bool have = take(cur);
+        int f = 0;
+        bool alive = true;
+        while (have && alive) {
+            const bool have_next = take(nxt);   // its loads complete while this item's chunks go out
+            for (int c = 0; c < p.nch; ++c, ++f) {
+                const int slot = f % M2_NSTG;
+                const long long st_t0 = M2STAT_NOW();
+                if (f >= M2_NSTG && !mbar_wait(&empty_bar[s][slot], ((f / M2_NSTG) - 1) & 1)) {
+                    if (lane == 0) atomicExch(p.err, 1);
+                    alive = false;
+                    break;
                 }
-                // is the set's next stage free?  One lane polls, so that the warp cannot split on the answer.
-                const int slot = s_f[s] % M2_NSTG;
-                int is_free = 1;
-                if (s_f[s] >= M2_NSTG) {
-                    if (lane == 0) is_free = mbar_try_wait(&empty_bar[s][slot], ((s_f[s] / M2_NSTG) - 1) & 1) ? 1 : 0;
-                    is_free = __shfl_sync(0xffffffffu, is_free, 0);
-                }
-                if (!is_free) continue;
-                progress = true;
+                const long long st_t1 = M2STAT_NOW();
                 M2Meta &m = meta[s][slot];
-                if (s_state[s] == 0) {
-                    // nothing left: tell the set to stop
-                    if (lane == 0) {
-                        m.flags = 2;
-                        mbar_arrive(&full_bar[s][slot]);
-                    }
-                    s_state[s] = 2;
-                    ++s_f[s];
-                    continue;
-                }
-                const int c = s_c[s];
                 uint8_t *stage = smem + (size_t)(s * M2_NSTG + slot) * p.stage_bytes;
                 uint8_t *q8dst = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
                 uint32_t bytes = 0;
                 if (lane == 0) {
-                    m.expert = s_e[s]; m.r0 = s_r0[s]; m.nrows = s_nrows[s]; m.ntok = s_ntok[s];
+                    m.expert = cur.e; m.r0 = cur.r0; m.nrows = cur.nrows; m.ntok = cur.ntok;
                     m.chunk = c; m.flags = c + 1 == p.nch ? 1 : 0;
                     m.w0_off = 0; m.w1_off = 0;
                     if (p.tiled) {
                         // the box is always 32 full rows of `pitch` bytes: rows past the expert's last and bytes past
                         // the row's end arrive as zeros
                         const int x = (c * p.cbytes) >> 3;   // the maps count in 8-byte elements
-                        tma_load_chunk(stage, &p.tm0, x, s_r0[s], s_e[s], &full_bar[s][slot]);
-                        if (DUAL) tma_load_chunk(stage + p.wtile_bytes, &p.tm1, x, s_r0[s], s_e[s], &full_bar[s][slot]);
+                        tma_load_chunk(stage, &p.tm0, x, cur.r0, cur.e, &full_bar[s][slot]);
+                        if (DUAL) tma_load_chunk(stage + p.wtile_bytes, &p.tm1, x, cur.r0, cur.e, &full_bar[s][slot]);
                         bytes = (uint32_t)(M2_R * p.pitch) * (DUAL ? 2u : 1u);
                     } else {
-                        const size_t g0 = (size_t)s_e[s] * p.stride0 + (size_t)s_r0[s] * p.rb;
-                        bytes += issue_tile(stage, p.w0, p.total0, g0, g0 + (size_t)s_nrows[s] * p.rb, &full_bar[s][slot], &m.w0_off);
+                        const size_t g0 = (size_t)cur.e * p.stride0 + (size_t)cur.r0 * p.rb;
+                        bytes += issue_tile(stage, p.w0, p.total0, g0, g0 + (size_t)cur.nrows * p.rb, &full_bar[s][slot], &m.w0_off);
                         if (DUAL) {
-                            const size_t h0 = (size_t)s_e[s] * p.stride1 + (size_t)s_r0[s] * p.rb;
-                            bytes += issue_tile(stage + p.wtile_bytes, p.w1, p.total1, h0, h0 + (size_t)s_nrows[s] * p.rb,
+                            const size_t h0 = (size_t)cur.e * p.stride1 + (size_t)cur.r0 * p.rb;
+                            bytes += issue_tile(stage + p.wtile_bytes, p.w1, p.total1, h0, h0 + (size_t)cur.nrows * p.rb,
                                                 &full_bar[s][slot], &m.w1_off);
                         }
                     }
                 }
-                if (lane < s_ntok[s]) {
+                if (lane < cur.ntok) {
                     // this chunk's slice of the pair's packed activation row, laid out as a row of I_l elements
-                    const int my_pair = s_pair[s];
-                    m.pair[lane] = my_pair;
-                    const uint8_t *src = p.q8 + (size_t)(my_pair / p.xdiv) * p.q8_stride;
+                    m.pair[lane] = cur.pair;
+                    const uint8_t *src = p.q8 + (size_t)(cur.pair / p.xdiv) * p.q8_stride;
                     uint8_t *dst = q8dst + (size_t)lane * p.q8s_l;
                     if (p.nch == 1) {
                         bulk_g2s(dst, src, (uint32_t)p.q8_stride, &full_bar[s][slot]);
@@ -249,21 +237,25 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 1), 1) mmid2_kernel(const __gri
                 }
                 __syncwarp();
                 // the producer's own arrival, with the byte count, is what lets the phase complete
-                if (lane == 0) mbar_arrive_expect_tx(&full_bar[s][slot], bytes + (uint32_t)s_ntok[s] * act_bytes);
-                ++s_f[s];
-                if (++s_c[s] == p.nch) s_state[s] = 0;
+                if (lane == 0) mbar_arrive_expect_tx(&full_bar[s][slot], bytes + (uint32_t)cur.ntok * act_bytes);
+                st_idle += st_t1 - st_t0;
+                st_busy += M2STAT_NOW() - st_t1;
+                ++st_fills;
             }
-            if (all_done) break;
-            if (progress) {
-                idle = 0;
-            } else {
-                if (++idle > (1 << 20)) {
-                    if (lane == 0) atomicExch(p.err, 1);
-                    break;
-                }
-                __nanosleep(40);
+            cur = nxt;
+            have = have_next;
+        }
+        // nothing left: tell the set to stop
+        if (alive) {
+            const int slot = f % M2_NSTG;
+            if (f >= M2_NSTG && !mbar_wait(&empty_bar[s][slot], ((f / M2_NSTG) - 1) & 1)) {
+                if (lane == 0) atomicExch(p.err, 1);
+            } else if (lane == 0) {
+                meta[s][slot].flags = 2;
+                mbar_arrive(&full_bar[s][slot]);
             }
         }
+        M2STAT_ADD(2, st_idle); M2STAT_ADD(3, st_busy); M2STAT_ADD(4, st_fills);
     } else {
         // ------------------------------ consumers -----------------------------
         const int set = warp / M2_WPS, ws = warp % M2_WPS;
@@ -286,12 +278,16 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 1), 1) mmid2_kernel(const __gri
             if (half == 0) hb1 = mid; else hb0 = mid;
         }
         int fcount = 0, n_mma = 0;
+        long long st_wait = 0, st_work = 0;
         for (;;) {
             const int slot = fcount % M2_NSTG;
+            const long long st_t0 = M2STAT_NOW();
             if (!mbar_wait(&full_bar[set][slot], (fcount / M2_NSTG) & 1)) {
                 if (lane == 0) atomicExch(p.err, 2);
                 break;
             }
+            const long long st_t1 = M2STAT_NOW();
+            st_wait += st_t1 - st_t0;
             const M2Meta &m = meta[set][slot];
             const int flags = m.flags;
             if (flags & 2) break;
@@ -317,6 +313,32 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 1), 1) mmid2_kernel(const __gri
                 if (piece * 16 < m_nrows && hb0 < hb1)
                     mma_rows<TYPE, false>((DUAL && half ? t1 : t0) + (uint32_t)(piece * 16) * p.pitch - (uint32_t)(ab * BB), 0, p.pitch,
                                           q8base, p.q8s_l, p.I_l, hb0 + 2 * ab, hb1 + 2 * ab, lane, f0, f0);
+            } else if (TYPE == Q2_K && upl == 4) {
+                // a lane's four units are one super-block: the block-at-a-time form
+                if (bl < p.cb) {
+#pragma unroll
+                    for (int tk = 0; tk < MMID_MAXTOK; ++tk) {
+                        if (tk < m_ntok) {
+#pragma unroll
+                            for (int pp = 0; pp < 2; ++pp) {
+                                if (pp < np) {
+                                    const uint32_t roff = (uint32_t)(pp * M2_WPS * rpp + ws * rpp + rl) * p.pitch + (uint32_t)bl * BB;
+                                    if (DUAL) {
+                                        const uint32_t blk[2] = {t0 + roff, t1 + roff};
+                                        float a[2] = {acc[pp][0][tk], acc[pp][1][tk]};
+                                        q2k_block_dot<2>(blk, q8base + tk * p.q8s_l, p.I_l, ab + bl, a);
+                                        acc[pp][0][tk] = a[0]; acc[pp][1][tk] = a[1];
+                                    } else {
+                                        const uint32_t blk[1] = {t0 + roff};
+                                        float a[1] = {acc[pp][0][tk]};
+                                        q2k_block_dot<1>(blk, q8base + tk * p.q8s_l, p.I_l, ab + bl, a);
+                                        acc[pp][0][tk] = a[0];
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
             } else {
 #pragma unroll
                 for (int tk = 0; tk < MMID_MAXTOK; ++tk) {
@@ -410,7 +432,9 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 1), 1) mmid2_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[set][slot]);
             ++fcount;
+            st_work += M2STAT_NOW() - st_t1;
         }
+        M2STAT_ADD(0, st_wait); M2STAT_ADD(1, st_work); M2STAT_ADD(5, fcount);
     }
 }
 

@@ -206,6 +206,82 @@ __device__ __forceinline__ void unit_dot(uint32_t blk, int sub, const UnitAct &a
     }
 }
 
+// One whole Q2_K super-block of one row (of two rows, NM = 2: the same block of the gate and of the up matrix)
+// against one activation block.  Same integers as four unit_dot calls; the work that does not depend on the unit
+// is done once per block: one load of d / dmin, the sixteen scale nibbles taken in place (a dp2a pairs the sums of
+// the two units h = 0, 1 of a 32-byte group with two adjacent scale bytes, so no byte is moved), the mins against
+// the group sums straight from the packed row, one int -> float conversion per sum.
+//   blk[m]: the block in shared memory (4-byte aligned); arow: the packed activation row; b: its block index
+//   acc[m] += d * d8 * isum - dmin * d8 * msum
+template <int NM>
+__device__ __forceinline__ void q2k_block_dot(const uint32_t (&blk)[NM], uint32_t arow, int I, int b, float (&acc)[NM]) {
+    uint32_t sc[NM][4];
+    int isum[NM];
+#pragma unroll
+    for (int m = 0; m < NM; ++m) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) sc[m][w] = lds32(blk[m] + 4 * w);
+        isum[m] = 0;
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+        // the two units of this half: aq[h][4 * j + i] multiplies word i of the 16 bytes h, plane j
+        uint32_t aq[2][16];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t base = arow + Q8_UNIT_STRIDE * (4 * b + 2 * n + h);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 v = lds128(base + 16 * j);
+                aq[h][4 * j + 0] = v.x; aq[h][4 * j + 1] = v.y; aq[h][4 * j + 2] = v.z; aq[h][4 * j + 3] = v.w;
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+            uint32_t qs[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qs[i] = lds32(blk[m] + 16 + 32 * n + 4 * i);
+            int S[4][2];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    int t = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) t = dp4a_us(qs[4 * h + i] & (0x03030303u << (2 * j)), (int)aq[h][4 * j + i], t);
+                    S[j][h] = t >> (2 * j);
+                }
+            }
+            const uint32_t s0 = sc[m][2 * n] & 0x0F0F0F0Fu, s1 = sc[m][2 * n + 1] & 0x0F0F0F0Fu;
+            int t = isum[m];
+            t = dp2a_lo_su(pack16(S[0][0], S[0][1]), s0, t);
+            t = dp2a_hi_su(pack16(S[1][0], S[1][1]), s0, t);
+            t = dp2a_lo_su(pack16(S[2][0], S[2][1]), s1, t);
+            t = dp2a_hi_su(pack16(S[3][0], S[3][1]), s1, t);
+            isum[m] = t;
+        }
+    }
+    // mins: word w of the group sums holds groups 2w, 2w + 1; byte g of the min nibbles is group g
+    const uint32_t bs = arow + q8row_bs_off(I) + 32 * b;
+    const uint4 b0 = lds128(bs), b1 = lds128(bs + 16);
+    const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    const float d8 = __uint_as_float(lds32(arow + q8row_d_off(I) + 4 * b));
+#pragma unroll
+    for (int m = 0; m < NM; ++m) {
+        int ms = 0;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t mn = (sc[m][w] >> 4) & 0x0F0F0F0Fu;
+            ms = dp2a_lo_su(bw[2 * w], mn, ms);
+            ms = dp2a_hi_su(bw[2 * w + 1], mn, ms);
+        }
+        const uint32_t dd = lds32(blk[m] + 80);
+        const float d = half_bits_to_float(dd), dmin = half_bits_to_float(dd >> 16);
+        acc[m] = fmaf(d * d8, (float)isum[m], acc[m]);
+        acc[m] = fmaf(-(dmin * d8), (float)ms, acc[m]);
+    }
+}
+
 // IQ2_XXS codebook (ggml data; reference backends/cpu/ggml_grids.cpp:11-15)
 static __device__ const uint64_t k_iq2xxs_grid[256] = {
 #include "iq2xxs_grid.inc"
