@@ -395,6 +395,13 @@ int zmoe_quantize_q8_K(const float *x_dev, void *blocks_dev, int rows, int I, in
  * isum = sum scale*(q.q8), msum = sum min*bsum; outputs [rows, I/256] i32 */
 int zmoe_block_isums(int type, const void *w_dev, const float *x_dev, int32_t *isum_dev, int32_t *msum_dev, int rows,
                      int I, void *stream);
+/* the same sums as the tensor-core consumer path of the decode kernels forms them (mma.sync on a 16-row piece
+ * against `pairs` <= 4 activation rows at once): w_dev = 16 weight rows, x_dev [pairs, I];
+ * sums_dev [16 rows][4 pair slots][I/256][2] i32 holds {isum, msum} of row r against activation row p at
+ * [r][p][block]; slots p >= pairs are scratch.  Q2_K, Q3_K (msum = 0), Q4_K; ZMOE_ERR_TYPE for a type without
+ * that path. */
+int zmoe_block_isums_pairs(int type, const void *w_dev, const float *x_dev, int32_t *sums_dev, int pairs, int I,
+                           void *stream);
 
 #ifdef __cplusplus
 }

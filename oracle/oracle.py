@@ -66,6 +66,9 @@ def lib():
         L.zo_router_min_margin.restype = C.c_float
         L.zo_moe_ffn.restype = C.c_int
         L.zo_moe_ffn_fast.restype = C.c_int
+        L.zo_fast_kind.restype = C.c_int
+        L.zo_fast_force.argtypes = [C.c_int]
+        L.zo_fast_force.restype = None
         _lib = L
     return _lib
 
@@ -242,6 +245,19 @@ def make_layer(D, F, E, K, types, w_gate, w_up, w_down, strides=None, clamp=0.0,
               strides[0], strides[1], strides[2], clamp, fused)
     L._keep = (w_gate, w_up, w_down)
     return L
+
+
+FAST_KINDS = {0: "scalar", 1: "AVX2", 2: "AVX-512 VNNI"}
+
+
+def fast_kind():
+    """the instruction set the timed CPU baseline (vec_dot "fast", moe_ffn(fast=True)) runs its dots on"""
+    return FAST_KINDS[lib().zo_fast_kind()]
+
+
+def fast_force(kind):
+    """tests: cap the baseline's instruction set (0 scalar, 1 AVX2, 2 AVX-512 VNNI; -1 the best the CPU has)"""
+    lib().zo_fast_force(kind)
 
 
 def moe_ffn(layer, x, ids, weights, want_act=False, fast=False, threads=0):

@@ -142,6 +142,10 @@ int zo_moe_ffn(const zo_layer *L, const float *x, const int32_t *ids, const floa
 int zo_moe_ffn_fast(const zo_layer *L, const float *x, const int32_t *ids, const float *weights,
                     int T, float *out, int n_threads);
 int zo_have_avx2(void);
+/* which dots zo_vec_dot_q8_K_fast / zo_moe_ffn_fast run: 0 scalar, 1 AVX2, 2 AVX-512 VNNI (bit-identical results) */
+int zo_fast_kind(void);
+/* tests: cap the kind (-1: the best the CPU has) */
+void zo_fast_force(int kind);
 
 #ifdef __cplusplus
 }

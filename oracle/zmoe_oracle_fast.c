@@ -1,9 +1,10 @@
 /*
  * zmoe_oracle_fast.c -- the timed CPU baseline: the same arithmetic as
- * zmoe_oracle.c with AVX2 integer dots and OpenMP over weight rows.
+ * zmoe_oracle.c with vector integer dots (AVX-512 VNNI where the CPU has it,
+ * else AVX2, else scalar) and OpenMP over weight rows.
  * TEST / BENCHMARK INFRASTRUCTURE ONLY; never linked into the shipped library.
  *
- * Instruction selection follows what the reference's CPU path runs: the pinned
+ * The AVX2 forms follow what the reference's CPU path runs: the pinned
  * ggml uses its AVX2 kernels for these types on x86 (reference
  * bench/q2k_dot_bench.cpp:33 labels the Q2_K one "stock"; bench/q3k_q4k_dot_bench.cpp:1-3).
  * Rows are grouped by expert like reference core/batched_dispatch_pipeline.cpp:1185-1204.
@@ -181,10 +182,138 @@ TGT static float dot_iq2xxs(int n, const blk_iq2_xxs *x, const blk_q8_K *y) {
     return 0.125f * hsum8v(acc);
 }
 
+/* ---------------------------------------------------------------------------------------------------
+ * AVX-512 VNNI forms of the K-quant dots.  The integer part runs on 64 bytes at a time with vpdpbusd; its 16 int32
+ * lanes fold onto the 8 lanes the AVX2 form keeps (lane l and lane l + 8 hold the same four element positions of
+ * two adjacent 32-element planes), so the int32 vector that is converted and accumulated in f32 is the same vector,
+ * and the result is bit-identical to the AVX2 form and to the scalar oracle.
+ * ------------------------------------------------------------------------------------------------- */
+#define TGT512 __attribute__((target("avx512f,avx512bw,avx512vl,avx512vnni,avx2,fma")))
+
+static int force_kind = -1;   /* tests: 0 scalar, 1 AVX2, 2 AVX-512 VNNI; -1 the best the CPU has */
+int zo_fast_kind(void) {
+    int best = 0;
+    if (zo_have_avx2()) best = 1;
+    if (best == 1 && __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512bw") &&
+        __builtin_cpu_supports("avx512vl") && __builtin_cpu_supports("avx512vnni"))
+        best = 2;
+    return force_kind >= 0 && force_kind < best ? force_kind : best;
+}
+void zo_fast_force(int kind) { force_kind = kind; }
+
+TGT512 static inline __m256i fold512(__m512i v) {
+    return _mm256_add_epi32(_mm512_castsi512_si256(v), _mm512_extracti64x4_epi64(v, 1));
+}
+/* 16-bit shift counts: `lo` in the low 256 bits, `hi` in the high 256 bits */
+TGT512 static inline __m512i shift_pair(int lo, int hi) {
+    return _mm512_inserti64x4(_mm512_set1_epi16((short)lo), _mm256_set1_epi16((short)hi), 1);
+}
+
+TGT512 static float dot_q2k_vnni(int n, const blk_q2_K *x, const blk_q8_K *y) {
+    const __m512i m3 = _mm512_set1_epi8(3);
+    /* 16-bit lane l of plane pair jp takes the scale of group g0 + l / 8 */
+    const __m512i grp = _mm512_srli_epi16(_mm512_set_epi16(31, 30, 29, 28, 27, 26, 25, 24, 23, 22, 21, 20, 19, 18, 17, 16, 15, 14,
+                                                           13, 12, 11, 10, 9, 8, 7, 6, 5, 4, 3, 2, 1, 0), 3);
+    __m256 acc = _mm256_setzero_ps();
+    for (int i = 0; i < n / 256; ++i) {
+        const float d = y[i].d * zo_fp16_to_fp32(x[i].d);
+        const float dmin = -y[i].d * zo_fp16_to_fp32(x[i].dmin);
+        const __m128i sb = _mm_loadu_si128((const __m128i *)x[i].scales);
+        const __m128i mn8 = _mm_and_si128(_mm_srli_epi16(sb, 4), _mm_set1_epi8(0xF));
+        const __m256i pm = _mm256_madd_epi16(_mm256_cvtepi8_epi16(mn8),
+                                             _mm256_loadu_si256((const __m256i *)y[i].bsums));
+        acc = _mm256_fmadd_ps(_mm256_set1_ps(dmin), _mm256_cvtepi32_ps(pm), acc);
+        /* the sixteen 4-bit scales as 16-bit values */
+        const __m512i sc16 = _mm512_castsi256_si512(_mm256_cvtepu8_epi16(_mm_and_si128(sb, _mm_set1_epi8(0xF))));
+        __m512i sumi = _mm512_setzero_si512();
+        for (int h = 0; h < 2; ++h) {
+            const __m512i qb = _mm512_broadcast_i64x4(_mm256_loadu_si256((const __m256i *)(x[i].qs + 32 * h)));
+            for (int jp = 0; jp < 2; ++jp) {
+                /* planes j = 2 jp (low half) and 2 jp + 1 (high half); two bytes of a 16-bit lane share a group,
+                 * and 3 * 15 fits a byte, so one 16-bit multiply scales both */
+                const __m512i q = _mm512_and_si512(_mm512_srlv_epi16(qb, shift_pair(4 * jp, 4 * jp + 2)), m3);
+                const __m512i sc = _mm512_permutexvar_epi16(_mm512_add_epi16(grp, _mm512_set1_epi16((short)(8 * h + 4 * jp))), sc16);
+                const __m512i a = _mm512_loadu_si512((const void *)(y[i].qs + 128 * h + 64 * jp));
+                sumi = _mm512_dpbusd_epi32(sumi, _mm512_mullo_epi16(q, sc), a);
+            }
+        }
+        acc = _mm256_fmadd_ps(_mm256_set1_ps(d), _mm256_cvtepi32_ps(fold512(sumi)), acc);
+    }
+    return hsum8v(acc);
+}
+
+TGT512 static float dot_q3k_vnni(int n, const blk_q3_K *x, const blk_q8_K *y) {
+    const __m512i m3 = _mm512_set1_epi8(3), one = _mm512_set1_epi8(1), four = _mm512_set1_epi8(4);
+    const __m512i grp = _mm512_srli_epi32(_mm512_set_epi32(15, 14, 13, 12, 11, 10, 9, 8, 7, 6, 5, 4, 3, 2, 1, 0), 2);
+    __m256 acc = _mm256_setzero_ps();
+    for (int i = 0; i < n / 256; ++i) {
+        const float d = y[i].d * zo_fp16_to_fp32(x[i].d);
+        int8_t sc[16];
+        q3k_scales16(x[i].scales, sc);
+        const __m512i sc32 = _mm512_cvtepi8_epi32(_mm_loadu_si128((const __m128i *)sc));
+        const __m512i hm = _mm512_broadcast_i64x4(_mm256_loadu_si256((const __m256i *)x[i].hmask));
+        __m512i sumi = _mm512_setzero_si512();
+        for (int h = 0; h < 2; ++h) {
+            const __m512i qb = _mm512_broadcast_i64x4(_mm256_loadu_si256((const __m256i *)(x[i].qs + 32 * h)));
+            for (int jp = 0; jp < 2; ++jp) {
+                const __m512i q2 = _mm512_and_si512(_mm512_srlv_epi16(qb, shift_pair(4 * jp, 4 * jp + 2)), m3);
+                const __m512i hb = _mm512_and_si512(_mm512_srlv_epi16(hm, shift_pair(4 * h + 2 * jp, 4 * h + 2 * jp + 1)), one);
+                const __m512i q = _mm512_or_si512(q2, _mm512_slli_epi16(hb, 2));      /* 0 .. 7 */
+                const __m512i a = _mm512_loadu_si512((const void *)(y[i].qs + 128 * h + 64 * jp));
+                /* (q - 4) . a per four elements, times the signed 6-bit scale of the lane's group */
+                const __m512i dp = _mm512_sub_epi32(_mm512_dpbusd_epi32(_mm512_setzero_si512(), q, a),
+                                                    _mm512_dpbusd_epi32(_mm512_setzero_si512(), four, a));
+                const __m512i scl = _mm512_permutexvar_epi32(_mm512_add_epi32(grp, _mm512_set1_epi32(8 * h + 4 * jp)), sc32);
+                sumi = _mm512_add_epi32(sumi, _mm512_mullo_epi32(dp, scl));
+            }
+        }
+        acc = _mm256_fmadd_ps(_mm256_set1_ps(d), _mm256_cvtepi32_ps(fold512(sumi)), acc);
+    }
+    return hsum8v(acc);
+}
+
+TGT512 static float dot_q4k_vnni(int n, const blk_q4_K *x, const blk_q8_K *y) {
+    const __m512i m4 = _mm512_set1_epi8(0xF);
+    __m256 acc = _mm256_setzero_ps();
+    float am[4] = {0, 0, 0, 0};
+    for (int i = 0; i < n / 256; ++i) {
+        const float d = y[i].d * zo_fp16_to_fp32(x[i].d);
+        const float dmin = -y[i].d * zo_fp16_to_fp32(x[i].dmin);
+        int sc[8], mn[8];
+        for (int j = 0; j < 8; ++j) q4k_sm(j, x[i].scales, &sc[j], &mn[j]);
+        for (int l = 0; l < 4; ++l) {
+            const int p = mn[2 * l] * (int)(int16_t)(y[i].bsums[4 * l] + y[i].bsums[4 * l + 1]) +
+                          mn[2 * l + 1] * (int)(int16_t)(y[i].bsums[4 * l + 2] + y[i].bsums[4 * l + 3]);
+            am[l] = fmaf(dmin, (float)p, am[l]);
+        }
+        __m512i sumi = _mm512_setzero_si512();
+        for (int c = 0; c < 4; ++c) {
+            /* low nibbles (elements 64c .. 64c+31) in the low half, high nibbles (64c+32 ..) in the high half */
+            const __m512i qb = _mm512_broadcast_i64x4(_mm256_loadu_si256((const __m256i *)(x[i].qs + 32 * c)));
+            const __m512i q = _mm512_and_si512(_mm512_srlv_epi16(qb, shift_pair(0, 4)), m4);
+            const __m512i a = _mm512_loadu_si512((const void *)(y[i].qs + 64 * c));
+            const __m512i dp = _mm512_dpbusd_epi32(_mm512_setzero_si512(), q, a);
+            const __m512i scl = _mm512_inserti64x4(_mm512_set1_epi32(sc[2 * c]), _mm256_set1_epi32(sc[2 * c + 1]), 1);
+            sumi = _mm512_add_epi32(sumi, _mm512_mullo_epi32(dp, scl));
+        }
+        acc = _mm256_fmadd_ps(_mm256_set1_ps(d), _mm256_cvtepi32_ps(fold512(sumi)), acc);
+    }
+    return hsum8v(acc) + ((am[0] + am[2]) + (am[1] + am[3]));
+}
+
 /* exported for the bit-exactness test against the scalar oracle */
 float zo_vec_dot_q8_K_fast(int type, int n, const void *w, const void *q8) {
-    if (!zo_have_avx2()) return zo_vec_dot_q8_K(type, n, w, q8);
+    const int kind = zo_fast_kind();
+    if (kind == 0) return zo_vec_dot_q8_K(type, n, w, q8);
     init_signs();
+    if (kind == 2) {
+        switch (type) {
+        case ZO_TYPE_Q2_K: return dot_q2k_vnni(n, (const blk_q2_K *)w, (const blk_q8_K *)q8);
+        case ZO_TYPE_Q3_K: return dot_q3k_vnni(n, (const blk_q3_K *)w, (const blk_q8_K *)q8);
+        case ZO_TYPE_Q4_K: return dot_q4k_vnni(n, (const blk_q4_K *)w, (const blk_q8_K *)q8);
+        default: break;   /* IQ2_XXS: the table lookups dominate; the AVX2 form serves */
+        }
+    }
     switch (type) {
     case ZO_TYPE_Q2_K: return dot_q2k(n, (const blk_q2_K *)w, (const blk_q8_K *)q8);
     case ZO_TYPE_Q3_K: return dot_q3k(n, (const blk_q3_K *)w, (const blk_q8_K *)q8);

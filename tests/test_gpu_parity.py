@@ -74,6 +74,31 @@ def test_block_int32_sums_bit_exact(zlib, oracle, dev, qtype):
         assert np.array_equal(msum[r].cpu().numpy(), rm), (qtype, r)
 
 
+@pytest.mark.parametrize("qtype", [synth.Q2_K, synth.Q3_K, synth.Q4_K])
+@pytest.mark.parametrize("pairs", [2, 3, 4])
+@pytest.mark.parametrize("I", [1536, 4096])
+def test_tensor_core_path_int32_sums_bit_exact(zlib, oracle, dev, qtype, pairs, I):
+    """the s32 sums mma.sync forms for 16 rows x `pairs` activation rows equal the oracle's, block by block"""
+    import torch
+    rng = synth.rng_for(14, qtype, pairs, I)
+    nb = I // 256
+    w = synth.random_blocks(qtype, 16 * nb, rng).reshape(16, -1)
+    x = synth.activations(pairs, I, rng) * rng.uniform(0.1, 4.0, size=(pairs, 1)).astype(np.float32)
+    wd, xd = to_dev(w, dev), to_dev(x, dev)
+    sums = torch.zeros((16, 4, nb, 2), dtype=torch.int32, device=dev)
+    zlib.check(zlib.load().zmoe_block_isums_pairs(qtype, zlib.ptr(wd), zlib.ptr(xd), zlib.ptr(sums), pairs, I, None),
+               "zmoe_block_isums_pairs")
+    _sync()
+    got = sums.cpu().numpy()
+    q8 = oracle.quantize_q8_K(x)
+    for r in range(16):
+        for p in range(pairs):
+            ri, rm = oracle.block_isums(qtype, w[r], q8[p])
+            assert np.array_equal(got[r, p, :, 0], ri), (qtype, r, p)
+            assert np.array_equal(got[r, p, :, 1], rm), (qtype, r, p)
+    assert zlib.load().zmoe_block_isums_pairs(synth.IQ2_XXS, zlib.ptr(wd), zlib.ptr(xd), zlib.ptr(sums), pairs, I, None) == -2
+
+
 # ---------------------------------------------------------------------------
 # launch_*_matmul (reference kernel-launch ABI)
 # ---------------------------------------------------------------------------

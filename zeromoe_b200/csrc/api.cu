@@ -902,5 +902,18 @@ int zmoe_block_isums(int type, const void *w_dev, const float *x_dev, int32_t *i
     return rc;
 }
 
+int zmoe_block_isums_pairs(int type, const void *w_dev, const float *x_dev, int32_t *sums_dev, int pairs, int I, void *stream) {
+    if (!w_dev || !x_dev || !sums_dev || pairs < 1 || pairs > 4 || I <= 0 || I % QK_K) return ZMOE_ERR_ARG;
+    if (block_bytes(type) == 0) return ZMOE_ERR_TYPE;
+    DeviceScratch *s;
+    ScratchLock lock;
+    int rc = scratch_get(pairs, I, 1, pairs, &s, lock);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!rc) rc = launch_quantize_rows(x_dev, I, s->q8, pairs, I, q8_layout_of(type), st);
+    if (!rc) rc = launch_mma_isums(type, w_dev, s->q8, sums_dev, I, pairs, st);
+    g_launches += 2;
+    return rc;
+}
+
 }  // extern "C"
 

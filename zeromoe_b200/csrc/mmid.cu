@@ -210,6 +210,43 @@ static int launch_mmid2(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st)
     return launch_pdl(fn, dim3(L.n_sm), dim3(32 * (M2_NCW + 4)), g.smem_bytes, st, p) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
 }
 
+// Parity hook of the tensor-core consumer path: one warp runs mma_rows on 16 weight rows against up to MMA_NTOK
+// packed activation rows and writes the per-super-block s32 sums.
+template <int TYPE>
+__global__ void __launch_bounds__(32) mma_isums_kernel(const uint8_t *w, const uint8_t *q8, int *out, int I, int pairs, int q8s) {
+    extern __shared__ __align__(128) uint8_t sm[];
+    constexpr int BB = QTraits<TYPE>::kBytes;
+    const int nb = I / QK_K, rb = nb * BB, qstride = q8row_stride(I);
+    uint8_t *wdst = sm, *qdst = sm + ((16 * rb + 127) & ~127);
+    for (int i = threadIdx.x; i < 16 * rb; i += 32) wdst[i] = w[i];
+    // slots past `pairs` repeat row 0: their sums are computed and never read
+    for (int t = 0; t < MMA_NTOK; ++t)
+        for (int i = threadIdx.x; i < qstride; i += 32) qdst[(size_t)t * q8s + i] = q8[(size_t)(t < pairs ? t : 0) * qstride + i];
+    __syncwarp();
+    float f[4] = {0.f, 0.f, 0.f, 0.f};
+    mma_rows<TYPE, false, true>(smem_u32(wdst), 0, rb, smem_u32(qdst), q8s, I, 0, 2 * nb, (int)threadIdx.x, f, f, out);
+}
+
+int launch_mma_isums(int type, const void *w, const uint8_t *q8, int *out, int I, int pairs, cudaStream_t st) {
+    if (pairs < 1 || pairs > MMA_NTOK) return ZMOE_ERR_ARG;
+    const int nb = I / QK_K, rb = nb * block_bytes(type);
+    if (rb % 4 != 0) return ZMOE_ERR_SHAPE;
+    int q8s = q8row_stride(I);
+    while ((q8s / 4) % 16 == 0) q8s += 16;
+    const size_t smem = (size_t)((16 * rb + 127) & ~127) + (size_t)MMA_NTOK * q8s;
+    if (smem > 200 * 1024) return ZMOE_ERR_SHAPE;
+    void (*fn)(const uint8_t *, const uint8_t *, int *, int, int, int) = nullptr;
+    switch (type) {
+    case Q2_K: fn = mma_isums_kernel<Q2_K>; break;
+    case Q3_K: fn = mma_isums_kernel<Q3_K>; break;
+    case Q4_K: fn = mma_isums_kernel<Q4_K>; break;
+    default: return ZMOE_ERR_TYPE;   // no tensor-core consumer path for the type
+    }
+    if (raise_dynamic_smem(reinterpret_cast<const void *>(fn), 200 * 1024) != ZMOE_OK) return ZMOE_ERR_CUDA;
+    fn<<<1, 32, smem, st>>>(static_cast<const uint8_t *>(w), q8, out, I, pairs, q8s);
+    return cudaPeekAtLastError() == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+}
+
 int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st) {
     if (g.v2) return launch_mmid2(L, g, st);
     int mma_ks = 0, mma_hpw = 0;

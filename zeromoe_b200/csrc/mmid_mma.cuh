@@ -259,9 +259,24 @@ template <> struct MmaPath<Q4_K> { static constexpr bool kHas = true; static con
 // Rows g and g+8 of a 16-row slice against the item's pairs over half-blocks [hb0, hb1): the f32 sums of
 // (row g, pair 2c), (row g, pair 2c+1), (row g+8, pair 2c), (row g+8, pair 2c+1) are added into f0 (tile0)
 // and, for DUAL, f1 (tile1).  Lanes with c >= MMA_NTOK / 2 return sums of repeated columns: ignore them.
-template <int TYPE, bool DUAL>
+// DBG (the parity hook of the integer stage): the per-super-block s32 sums of tile0 are also written to
+// dbg[((row * MMA_NTOK + pair) * (I / 256) + block) * 2 + {0: scale-weighted sum, 1: min-weighted sum}]; the range
+// [hb0, hb1) must then cover whole super-blocks.
+template <int TYPE, bool DUAL, bool DBG = false>
 __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb, uint32_t q8rows, int q8_stride, int I,
-                                         int hb0, int hb1, int lane, float (&f0)[4], float (&f1)[4]) {
+                                         int hb0, int hb1, int lane, float (&f0)[4], float (&f1)[4], int *dbg = nullptr) {
+    auto dbg_put = [&](int b, const int (&is)[4], const int (&ms)[4]) {
+        const int g_ = lane >> 2, c_ = lane & 3;
+        if (2 * c_ < MMA_NTOK) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row = g_ + 8 * (i >> 1), pair = 2 * c_ + (i & 1);
+                int *o = dbg + ((size_t)(row * MMA_NTOK + pair) * (I / 256) + b) * 2;
+                o[0] = is[i];
+                o[1] = ms[i];
+            }
+        }
+    };
     constexpr int BB = QTraits<TYPE>::kBytes;
     const int g = lane >> 2, c = lane & 3;
     const uint32_t offA = (uint32_t)g * rb, offB = (uint32_t)(g + 8) * rb;
@@ -293,6 +308,7 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
                 float (&f)[4] = m ? f1 : f0;
                 int cn[4];
                 q2k_mins(rowA, rowB, c, bs_hi, bs_lo, cn);
+                if (DBG && m == 0) dbg_put(b, cm, cn);
                 const uint32_t wa = lds32(rowA + 80), wb = lds32(rowB + 80);
                 const float dA = half_bits_to_float(wa), mA = half_bits_to_float(wa >> 16);
                 const float dB = half_bits_to_float(wb), mB = half_bits_to_float(wb >> 16);
@@ -321,6 +337,10 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
                 const uint32_t fa = c < 2 ? mnA[c & 1] : 0u, fb = c < 2 ? mnB[c & 1] : 0u;
                 mma_k16_zero<false>(hi, fa, fb, bs_hi);
                 mma_k16_zero<false>(cn, fa, fb, bs_lo);
+                if (DBG && m == 0) {
+                    const int mt[4] = {cn[0] + 128 * hi[0], cn[1] + 128 * hi[1], cn[2] + 128 * hi[2], cn[3] + 128 * hi[3]};
+                    dbg_put(b, cm, mt);
+                }
                 const uint32_t wa = lds32(rowA), wb = lds32(rowB);
                 const float dA = half_bits_to_float(wa), mA = half_bits_to_float(wa >> 16);
                 const float dB = half_bits_to_float(wb), mB = half_bits_to_float(wb >> 16);
@@ -369,6 +389,10 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
                     const uint32_t t = m ? tile1 : tile0;
                     int (&a)[4] = m ? a1 : a0;
                     float (&f)[4] = m ? f1 : f0;
+                    if (DBG && m == 0) {
+                        const int zero[4] = {0, 0, 0, 0};
+                        dbg_put(b, a, zero);
+                    }
                     const float dA = half_bits_to_float(lds16(t + offA + boff + 108));
                     const float dB = half_bits_to_float(lds16(t + offB + boff + 108));
                     f[0] = fmaf(dA * dx0, (float)a[0], f[0]);

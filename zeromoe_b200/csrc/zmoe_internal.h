@@ -111,6 +111,8 @@ struct MmidLaunch {
 // end of a row are out of bounds and arrive as zeros, which pads the rows in shared memory.  Rows up to 2032 bytes.
 int make_rows_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t expert_stride, int R);
 int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st);
+// s32 sums of the tensor-core consumer path: out[16 rows][4 pair slots][I / 256][2]
+int launch_mma_isums(int type, const void *w, const uint8_t *q8, int *out, int I, int pairs, cudaStream_t st);
 
 // prefill path: tcgen05 grouped GEMM over fp16 activations (Q8_K round trip applied, rows scaled)
 struct GemmLaunch {

@@ -24,7 +24,7 @@ EXPORTS = [
     "zmoe_ctx_create", "zmoe_ctx_destroy", "zmoe_layer_create", "zmoe_layer_destroy", "zmoe_route",
     "zmoe_set_routes", "zmoe_set_routes_strided", "zmoe_set_routes_window", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_dense_ffn", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
     "zmoe_get_expert_freq", "zmoe_copy_routes", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_set_path", "zmoe_ctx_check", "zmoe_kernel_launches",
-    "zmoe_quantize_q8_K", "zmoe_block_isums",
+    "zmoe_quantize_q8_K", "zmoe_block_isums", "zmoe_block_isums_pairs",
     "zmoe_device_status", "zmoe_selftest_wait_expiry", "zmoe_ctx_bad_counts", "zmoe_gemm_min_pairs_per_expert",
     "zmoe_debug_gemm_cycles",
     "zmoe_ep_unique_id", "zmoe_ep_comm_init", "zmoe_ep_comm_destroy", "zmoe_ep_create", "zmoe_ep_destroy",
@@ -117,6 +117,7 @@ def load():
     L.zmoe_route.argtypes = [vp, vp, i, vp]
     L.zmoe_set_routes.argtypes = [vp, vp, vp, vp, i, vp]
     L.zmoe_set_routes_window.argtypes = [vp, vp, vp, vp, i, i, vp]
+    L.zmoe_block_isums_pairs.argtypes = [i, vp, vp, vp, i, i, vp]
     L.zmoe_set_routes_strided.argtypes = [vp, vp, vp, C.c_size_t, vp, C.c_size_t, i, vp]
     L.zmoe_expert_ffn.argtypes = [vp, vp, i, i, vp]
     L.zmoe_expert_ffn_events.argtypes = [vp, vp, i, i, vp, vp, vp]
