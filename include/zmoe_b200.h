@@ -226,6 +226,10 @@ int zmoe_expert_ffn_events(zmoe_layer *layer, float *out_dev, int T, int accumul
  * accumulate = 1 the result is added to out_dev (the routed sum).  Overwrites the context's route
  * table. */
 int zmoe_dense_ffn(zmoe_layer *layer, const float *x_dev, float *out_dev, int T, int accumulate, void *stream);
+/* the same with the shared expert's scalar gate (reference models/graph/ggml_moe_graph_builder.cpp:120-124):
+ * every token's row is multiplied by sigmoid(gate_w . x[t]) before it is written or added; gate_w_dev [d_model] f32 */
+int zmoe_dense_ffn_gated(zmoe_layer *layer, const float *x_dev, const float *gate_w_dev, float *out_dev, int T,
+                         int accumulate, void *stream);
 /* zmoe_route followed by zmoe_expert_ffn */
 int zmoe_moe_forward(zmoe_layer *layer, const float *x_dev, float *out_dev, int T, void *stream);
 /* the same with host buffers: copies x in, runs the layer, copies out back, synchronises */

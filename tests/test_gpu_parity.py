@@ -519,6 +519,33 @@ def test_deepseek_shaped_layer_with_shared_expert(zlib, oracle, dev):
     assert rel_to_norm(out.cpu().numpy(), ref) < REL_TO_NORM
 
 
+def test_shared_expert_with_scalar_gate(zlib, oracle, dev):
+    """shared = sigmoid(W_gi . x) * FFN(x), added to what the output holds (reference
+    models/graph/ggml_moe_graph_builder.cpp:120-124)"""
+    import torch
+    D, F, T = 2048, 768, 6
+    types = (synth.Q4_K,) * 3
+    rng = synth.rng_for(31, 0)
+    sg = synth.expert_weights(types[0], 1, F, D, rng)
+    su = synth.expert_weights(types[1], 1, F, D, rng)
+    sd = synth.expert_weights(types[2], 1, D, F, rng)
+    x = synth.activations(T, D, rng)
+    gw = (rng.standard_normal(D) * 0.05).astype(np.float32)
+    base = rng.standard_normal((T, D)).astype(np.float32)
+    ctx = zlib.Context(16, D, F, 1, 1)
+    shared = zlib.Layer(ctx, D, F, 1, 1, types, to_dev(sg, dev), to_dev(su, dev), to_dev(sd, dev))
+    out = to_dev(base.copy(), dev)
+    shared.dense_ffn_gated(to_dev(x, dev), to_dev(gw, dev), out, accumulate=1)
+    _sync()
+    ctx.check()
+    raw = oracle.moe_ffn(oracle.make_layer(D, F, 1, 1, types, sg, su, sd), x, np.zeros((T, 1), np.int32),
+                         np.ones((T, 1), np.float32))
+    gate = 1.0 / (1.0 + np.exp(-(x.astype(np.float64) @ gw.astype(np.float64))))
+    ref = base + raw * gate[:, None].astype(np.float32)
+    assert rel_to_norm(out.cpu().numpy() - base, ref - base) < REL_TO_NORM
+    assert zlib.load().zmoe_dense_ffn_gated(shared.h, None, zlib.ptr(out), zlib.ptr(out), T, 0, None) == -1
+
+
 def test_moe_forward_host_buffers(zlib, oracle, dev):
     import torch
     D, F, E, K, T = 1024, 512, 16, 4, 4

@@ -114,6 +114,7 @@ struct zmoe_ctx {
     float *xscale = nullptr, *actscale = nullptr;  // per-row powers of two of the fp16 copies
     int32_t *zero_ids = nullptr;   // [T] zeros / ones: routes of a dense (single-expert) FFN
     float *one_w = nullptr;
+    float *gate_s = nullptr;       // [T] per-token scalar gates of a gated shared expert
     const float *x_last = nullptr;  // the activations the current route table was built from
     int path = 0;              // 0 auto, 1 decode kernels, 2 tensor-core GEMM, 3 decode kernels, scalar path only
     float *ydown = nullptr;    // [P, D] per-pair down-projection output
@@ -130,18 +131,27 @@ struct zmoe_ctx {
     cudaStream_t host_stream = nullptr;
     int *err_host = nullptr;   // pinned mirror of err: the host entry reads the flag with the same sync as its output
     int routed_t = -1;  // tokens of the current route table
+    bool plan_small = false;  // the current plan's items are those of the layer's `small` kernel set
 };
 
 struct zmoe_layer {
     zmoe_ctx *ctx;
     zmoe_layer_desc d;
-    MmidGeom g_gu, g_gate1, g_dn;
-    CUtensorMap tm_gate, tm_up, tm_down;   // padded-row tile maps, where the geometry pads rows
-    bool has_tm_gu = false, has_tm_dn = false;
+    // Geometries, tile maps and item spaces of the decode kernels.  Two sets: `big` (the K-chunked kernel where
+    // the shapes allow it) and `small` (the kernel whose whole CTA works on one 16-row item: shorter latency
+    // when there are fewer items than warp sets to give them to).  The plan of a call is built for one of them.
+    struct Proj {
+        MmidGeom g_gu, g_gate1, g_dn;
+        CUtensorMap tm_gate, tm_up, tm_down;
+        bool has_tm_gu = false, has_tm_dn = false;
+        int nrt_gu = 0, nrt_dn = 0;
+        int mt_gu = 4, mt_dn = 4;   // pairs per item of the two projections
+    } big, small;
     bool dual;
     size_t bytes_gate, bytes_up, bytes_down;
-    int nrt_gu, nrt_dn;
 };
+// calls with at most this many pairs take the `small` set
+static const int kSmallCallPairs = 8;
 
 namespace zmoe {
 int layer_route_table(zmoe_layer *L, const int32_t **ids_dev, const float **weights_dev, int *n_experts) {
@@ -178,6 +188,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     rc |= dev_alloc(&c->xscale, P);
     rc |= dev_alloc(&c->zero_ids, (size_t)max_tokens);
     rc |= dev_alloc(&c->one_w, (size_t)max_tokens);
+    rc |= dev_alloc(&c->gate_s, (size_t)max_tokens);
     rc |= dev_alloc(&c->actscale, P);
     rc |= dev_alloc(&c->ydown, P * max_d_model);
     rc |= dev_alloc(&c->logits, (size_t)max_tokens * max_experts);
@@ -219,7 +230,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
 
 void zmoe_ctx_destroy(zmoe_ctx *c) {
     if (!c) return;
-    cudaFree(c->zero_ids); cudaFree(c->one_w);
+    cudaFree(c->zero_ids); cudaFree(c->one_w); cudaFree(c->gate_s);
     cudaFree(c->xq_f16); cudaFree(c->actq_f16); cudaFree(c->xscale); cudaFree(c->actscale);
     cudaFree(c->q8x); cudaFree(c->q8x2); cudaFree(c->act); cudaFree(c->act2); cudaFree(c->q8act); cudaFree(c->ydown);
     cudaFree(c->logits); cudaFree(c->logits_part); cudaFree(c->ids); cudaFree(c->weights); cudaFree(c->err); cudaFree(c->bad); cudaFree(c->ticket);
@@ -228,6 +239,61 @@ void zmoe_ctx_destroy(zmoe_ctx *c) {
     if (c->host_stream) cudaStreamDestroy(c->host_stream);
     if (c->err_host) cudaFreeHost(c->err_host);
     delete c;
+}
+
+// geometries, item spaces and tile maps of one set of decode kernels for a layer
+static int build_proj(const zmoe_layer_desc &d, bool dual, bool allow_v2, zmoe_layer::Proj *P) {
+    int rc = mmid_geometry(d.gate.type, d.d_model, d.d_ff, dual, &P->g_gu, allow_v2);
+    if (!rc && !dual) {
+        rc = mmid_geometry(d.up.type, d.d_model, d.d_ff, false, &P->g_gate1, allow_v2);
+        // the two single projections share one item space: both on the K-chunked kernel (32-row items) or neither
+        if (!rc && P->g_gu.v2 != P->g_gate1.v2) {
+            rc = mmid_geometry(d.gate.type, d.d_model, d.d_ff, false, &P->g_gu, false);
+            if (!rc) rc = mmid_geometry(d.up.type, d.d_model, d.d_ff, false, &P->g_gate1, false);
+        }
+        if (!rc) {
+            // ... with the smaller tile and the fewer pairs per item of the two
+            if (P->g_gate1.R < P->g_gu.R) P->g_gu.R = P->g_gate1.R; else P->g_gate1.R = P->g_gu.R;
+            const int mt = P->g_gu.maxtok < P->g_gate1.maxtok ? P->g_gu.maxtok : P->g_gate1.maxtok;
+            P->g_gu.maxtok = mt; P->g_gate1.maxtok = mt;
+        }
+    }
+    if (!rc) rc = mmid_geometry(d.down.type, d.d_ff, d.d_model, false, &P->g_dn, allow_v2);
+    if (rc) return rc;
+    P->nrt_gu = (d.d_ff + P->g_gu.R - 1) / P->g_gu.R;
+    P->nrt_dn = (d.d_model + P->g_dn.R - 1) / P->g_dn.R;
+    P->mt_gu = P->g_gu.maxtok;
+    P->mt_dn = P->g_dn.maxtok;
+    const int rb_gu = (d.d_model / QK_K) * block_bytes(d.gate.type), rb_dn = (d.d_ff / QK_K) * block_bytes(d.down.type);
+    if (P->g_gu.v2) {
+        if (P->g_gu.tiled) {
+            P->has_tm_gu =
+                make_chunk_map(&P->tm_gate, d.gate.data_dev, d.n_experts, d.d_ff, rb_gu, d.gate.expert_stride, P->g_gu.pitch) == ZMOE_OK;
+            if (dual)
+                P->has_tm_gu = P->has_tm_gu && make_chunk_map(&P->tm_up, d.up.data_dev, d.n_experts, d.d_ff, rb_gu,
+                                                              d.up.expert_stride, P->g_gu.pitch) == ZMOE_OK;
+            if (!P->has_tm_gu) return ZMOE_ERR_CUDA;
+        }
+        if (!dual && P->g_gate1.tiled &&
+            make_chunk_map(&P->tm_up, d.up.data_dev, d.n_experts, d.d_ff, (d.d_model / QK_K) * block_bytes(d.up.type),
+                           d.up.expert_stride, P->g_gate1.pitch) != ZMOE_OK)
+            return ZMOE_ERR_CUDA;
+    } else if (dual && P->g_gu.rbs != rb_gu) {
+        P->has_tm_gu =
+            make_rows_map(&P->tm_gate, d.gate.data_dev, d.n_experts, d.d_ff, rb_gu, d.gate.expert_stride, P->g_gu.R) == ZMOE_OK &&
+            make_rows_map(&P->tm_up, d.up.data_dev, d.n_experts, d.d_ff, rb_gu, d.up.expert_stride, P->g_gu.R) == ZMOE_OK;
+    }
+    if (P->g_dn.v2) {
+        if (P->g_dn.tiled) {
+            P->has_tm_dn = make_chunk_map(&P->tm_down, d.down.data_dev, d.n_experts, d.d_model, rb_dn, d.down.expert_stride,
+                                          P->g_dn.pitch) == ZMOE_OK;
+            if (!P->has_tm_dn) return ZMOE_ERR_CUDA;
+        }
+    } else if (P->g_dn.rbs != rb_dn) {
+        P->has_tm_dn = make_rows_map(&P->tm_down, d.down.data_dev, d.n_experts, d.d_model, rb_dn, d.down.expert_stride,
+                                     P->g_dn.R) == ZMOE_OK;
+    }
+    return ZMOE_OK;
 }
 
 int zmoe_layer_create(zmoe_ctx *ctx, const zmoe_layer_desc *desc, zmoe_layer **out) {
@@ -243,20 +309,8 @@ int zmoe_layer_create(zmoe_ctx *ctx, const zmoe_layer_desc *desc, zmoe_layer **o
     L->ctx = ctx;
     L->d = d;
     L->dual = d.gate.type == d.up.type;
-    int rc = mmid_geometry(d.gate.type, d.d_model, d.d_ff, L->dual, &L->g_gu, true);
-    if (!rc && !L->dual) {
-        rc = mmid_geometry(d.up.type, d.d_model, d.d_ff, false, &L->g_gate1, true);
-        // the two single projections share one item space: both on the K-chunked kernel (32-row items) or neither
-        if (!rc && L->g_gu.v2 != L->g_gate1.v2) {
-            rc = mmid_geometry(d.gate.type, d.d_model, d.d_ff, false, &L->g_gu, false);
-            if (!rc) rc = mmid_geometry(d.up.type, d.d_model, d.d_ff, false, &L->g_gate1, false);
-        }
-        // both single projections share one item space: use the smaller tile for both
-        if (!rc) {
-            if (L->g_gate1.R < L->g_gu.R) L->g_gu.R = L->g_gate1.R; else L->g_gate1.R = L->g_gu.R;
-        }
-    }
-    if (!rc) rc = mmid_geometry(d.down.type, d.d_ff, d.d_model, false, &L->g_dn, true);
+    int rc = build_proj(d, L->dual, true, &L->big);
+    if (!rc) rc = build_proj(d, L->dual, false, &L->small);
     const zmoe_weight *ws[3] = {&d.gate, &d.up, &d.down};
     size_t *tot[3] = {&L->bytes_gate, &L->bytes_up, &L->bytes_down};
     for (int i = 0; i < 3 && !rc; ++i) {
@@ -271,37 +325,6 @@ int zmoe_layer_create(zmoe_ctx *ctx, const zmoe_layer_desc *desc, zmoe_layer **o
     if (rc) {
         delete L;
         return rc;
-    }
-    L->nrt_gu = (d.d_ff + L->g_gu.R - 1) / L->g_gu.R;
-    L->nrt_dn = (d.d_model + L->g_dn.R - 1) / L->g_dn.R;
-    {
-        const int rb_gu = (d.d_model / QK_K) * block_bytes(d.gate.type), rb_dn = (d.d_ff / QK_K) * block_bytes(d.down.type);
-        if (L->g_gu.v2) {
-            if (L->g_gu.tiled) {
-                L->has_tm_gu =
-                    make_chunk_map(&L->tm_gate, d.gate.data_dev, d.n_experts, d.d_ff, rb_gu, d.gate.expert_stride, L->g_gu.pitch) == ZMOE_OK;
-                if (L->dual)
-                    L->has_tm_gu = L->has_tm_gu && make_chunk_map(&L->tm_up, d.up.data_dev, d.n_experts, d.d_ff, rb_gu,
-                                                                  d.up.expert_stride, L->g_gu.pitch) == ZMOE_OK;
-                else if (L->g_gate1.tiled)
-                    L->has_tm_gu = L->has_tm_gu && make_chunk_map(&L->tm_up, d.up.data_dev, d.n_experts, d.d_ff,
-                                                                  (d.d_model / QK_K) * block_bytes(d.up.type), d.up.expert_stride,
-                                                                  L->g_gate1.pitch) == ZMOE_OK;
-                if (!L->has_tm_gu) rc = ZMOE_ERR_CUDA;
-            }
-        } else if (L->dual && L->g_gu.rbs != rb_gu)
-            L->has_tm_gu =
-                make_rows_map(&L->tm_gate, d.gate.data_dev, d.n_experts, d.d_ff, rb_gu, d.gate.expert_stride, L->g_gu.R) == ZMOE_OK &&
-                make_rows_map(&L->tm_up, d.up.data_dev, d.n_experts, d.d_ff, rb_gu, d.up.expert_stride, L->g_gu.R) == ZMOE_OK;
-        if (L->g_dn.v2) {
-            if (L->g_dn.tiled) {
-                L->has_tm_dn = make_chunk_map(&L->tm_down, d.down.data_dev, d.n_experts, d.d_model, rb_dn, d.down.expert_stride,
-                                              L->g_dn.pitch) == ZMOE_OK;
-                if (!L->has_tm_dn) rc = ZMOE_ERR_CUDA;
-            }
-        } else if (L->g_dn.rbs != rb_dn)
-            L->has_tm_dn = make_rows_map(&L->tm_down, d.down.data_dev, d.n_experts, d.d_model, rb_dn, d.down.expert_stride,
-                                         L->g_dn.R) == ZMOE_OK;
     }
     if (rc) {
         delete L;
@@ -351,7 +374,10 @@ int zmoe_route(zmoe_layer *L, const float *x_dev, int T, void *stream) {
     a.logits = c->logits; a.ids = c->ids; a.weights = c->weights; a.q8x = c->q8x;
     a.q8_layout = q8_layout_of(L->d.gate.type);
     a.plan = c->plan.b;
-    a.nrt_gu = L->nrt_gu; a.nrt_dn = L->nrt_dn;
+    c->plan_small = (long)T * L->d.topk <= kSmallCallPairs;
+    const zmoe_layer::Proj &ps = c->plan_small ? L->small : L->big;
+    a.plan.mt_gu = ps.mt_gu; a.plan.mt_dn = ps.mt_dn;
+    a.nrt_gu = ps.nrt_gu; a.nrt_dn = ps.nrt_dn;
     a.ticket = c->ticket;
     a.logits_part = c->logits_part;
     a.n_sm = c->n_sm;
@@ -384,9 +410,13 @@ static int set_routes_impl(zmoe_layer *L, const float *x_dev, const int32_t *ids
     c->q8x_valid = false;
     if (!takes_gemm(L, T)) rc = quantize_input(L, x_dev, T, st);   // the tensor-core path quantises while it gathers
     // the planner takes the routes in (copy, window mapping) before it groups them: one launch
+    PlanBuffers pb = c->plan.b;
+    c->plan_small = (long)P <= kSmallCallPairs;
+    const zmoe_layer::Proj &ps = c->plan_small ? L->small : L->big;
+    pb.mt_gu = ps.mt_gu; pb.mt_dn = ps.mt_dn;
     if (!rc)
         rc = launch_plan_ingest(ids_dev, weights_dev, c->ids, c->weights, (int)P, L->d.n_experts, first_expert, window,
-                                c->plan.b, L->nrt_gu, L->nrt_dn, st, ids_ld ? L->d.topk : 0, ids_ld, w_ld);
+                                pb, ps.nrt_gu, ps.nrt_dn, st, ids_ld ? L->d.topk : 0, ids_ld, w_ld);
     if (!rc) { g_launches += 1; c->routed_t = T; c->x_last = x_dev; }
     return rc;
 }
@@ -469,6 +499,7 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         rc = quantize_input(L, c->x_last, T, st);
         if (rc) return rc;
     }
+    const zmoe_layer::Proj &ps = c->plan_small ? L->small : L->big;   // the set the plan was built for
     if (ev_before) cudaEventRecord(static_cast<cudaEvent_t>(ev_before), st);
     if (L->dual) {
         m.type = d.gate.type; m.dual = true;
@@ -479,8 +510,8 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         m.q8 = c->q8x; m.xdiv = d.topk;
         m.y = c->act; m.ldy = d.d_ff;
         m.down = false;
-        if (L->has_tm_gu) { m.tm0 = &L->tm_gate; m.tm1 = &L->tm_up; }
-        rc = launch_mmid(m, L->g_gu, st);
+        if (ps.has_tm_gu) { m.tm0 = &ps.tm_gate; m.tm1 = &ps.tm_up; }
+        rc = launch_mmid(m, ps.g_gu, st);
         m.tm0 = nullptr; m.tm1 = nullptr;
         g_launches += 1;
     } else {
@@ -489,12 +520,12 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         m.I = d.d_model; m.O = d.d_ff; m.q8 = c->q8x; m.xdiv = d.topk; m.ldy = d.d_ff; m.down = false;
         m.type = d.up.type; m.w0 = d.up.data_dev; m.stride0 = d.up.expert_stride; m.total0 = L->bytes_up; m.y = ubuf;
         if (q8_layout_of(d.up.type) != q8_layout_of(d.gate.type)) m.q8 = c->q8x2;
-        m.tm0 = L->g_gate1.v2 && L->g_gate1.tiled ? &L->tm_up : nullptr;
-        rc = launch_mmid(m, L->g_gate1, st);
+        m.tm0 = ps.g_gate1.v2 && ps.g_gate1.tiled ? &ps.tm_up : nullptr;
+        rc = launch_mmid(m, ps.g_gate1, st);
         m.q8 = c->q8x;
         m.type = d.gate.type; m.w0 = d.gate.data_dev; m.stride0 = d.gate.expert_stride; m.total0 = L->bytes_gate; m.y = gbuf;
-        m.tm0 = L->g_gu.v2 && L->g_gu.tiled ? &L->tm_gate : nullptr;
-        if (!rc) rc = launch_mmid(m, L->g_gu, st);
+        m.tm0 = ps.g_gu.v2 && ps.g_gu.tiled ? &ps.tm_gate : nullptr;
+        if (!rc) rc = launch_mmid(m, ps.g_gu, st);
         m.tm0 = nullptr;
         if (!rc) {
             launch_expert_swiglu(c->act, gbuf, ubuf, P * d.d_ff, d.swiglu_clamp, d.swiglu_clamp_fused, c->bad, stream);
@@ -513,8 +544,8 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
         m.q8 = c->q8act; m.xdiv = 1;
         m.y = c->ydown; m.ldy = d.d_model;
         m.down = true;
-        if (L->has_tm_dn) m.tm0 = &L->tm_down;
-        rc = launch_mmid(m, L->g_dn, st);
+        if (ps.has_tm_dn) m.tm0 = &ps.tm_down;
+        rc = launch_mmid(m, ps.g_dn, st);
     }
     if (!rc) rc = launch_combine(out_dev, c->ydown, c->weights, c->ids, T, d.topk, d.d_model, d.n_experts, accumulate, st);
     g_launches += 3;
@@ -526,6 +557,19 @@ int zmoe_dense_ffn(zmoe_layer *L, const float *x_dev, float *out_dev, int T, int
     if (L->d.n_experts != 1 || L->d.topk != 1) return ZMOE_ERR_STATE;
     if (T > L->ctx->max_t) return ZMOE_ERR_CAPACITY;
     int rc = zmoe_set_routes(L, x_dev, L->ctx->zero_ids, L->ctx->one_w, T, stream);
+    if (!rc) rc = zmoe_expert_ffn(L, out_dev, T, accumulate, stream);
+    return rc;
+}
+
+int zmoe_dense_ffn_gated(zmoe_layer *L, const float *x_dev, const float *gate_w_dev, float *out_dev, int T, int accumulate,
+                         void *stream) {
+    if (!L || !x_dev || !gate_w_dev || !out_dev || T <= 0) return ZMOE_ERR_ARG;
+    if (L->d.n_experts != 1 || L->d.topk != 1) return ZMOE_ERR_STATE;
+    if (T > L->ctx->max_t) return ZMOE_ERR_CAPACITY;
+    // the scalar gate rides as the route weight: the combine multiplies each token's row by it
+    int rc = launch_token_gate(x_dev, gate_w_dev, L->ctx->gate_s, T, L->d.d_model, static_cast<cudaStream_t>(stream));
+    g_launches += 1;
+    if (!rc) rc = zmoe_set_routes(L, x_dev, L->ctx->zero_ids, L->ctx->gate_s, T, stream);
     if (!rc) rc = zmoe_expert_ffn(L, out_dev, T, accumulate, stream);
     return rc;
 }

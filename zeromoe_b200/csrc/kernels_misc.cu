@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const Rou
     if (s_ticket != n_tg - 1) return;
     __threadfence();
     PlanOut po{a.plan.hdr, a.plan.active, a.plan.offs, a.plan.slot, a.plan.item_offs_gu, a.plan.item_offs_dn,
-               a.plan.freq, a.plan.aoffs, a.plan.antok, a.nrt_gu, a.nrt_dn, a.plan.pos};
+               a.plan.freq, a.plan.aoffs, a.plan.antok, a.nrt_gu, a.nrt_dn, a.plan.pos, a.plan.mt_gu, a.plan.mt_dn};
     build_plan_cta(a.ids, a.T * a.K, a.E, po, cnt_s, pre_s, ids_s);
     if (tid == 0) a.ticket[0] = 0u;
 }
@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(1024) plan_from_ids_kernel(const int32_t *ids,
 static int launch_plan(const int32_t *ids, int P, int E, const PlanBuffers &plan, int nrt_gu, int nrt_dn,
                        const RouteIngest &in, cudaStream_t st) {
     PlanOut po{plan.hdr, plan.active, plan.offs, plan.slot, plan.item_offs_gu, plan.item_offs_dn, plan.freq,
-               plan.aoffs, plan.antok, nrt_gu, nrt_dn, plan.pos};
+               plan.aoffs, plan.antok, nrt_gu, nrt_dn, plan.pos, plan.mt_gu, plan.mt_dn};
     const size_t smem = (size_t)2 * (E + 1) * sizeof(int) + (P <= ROUTER_IDS_SMEM ? (size_t)P * sizeof(int) : 0);
     if (smem > 48 * 1024) return ZMOE_ERR_SHAPE;
     return launch_pdl(plan_from_ids_kernel, dim3(1), dim3(1024), smem, st, ids, P, E, po, in) == cudaSuccess
@@ -283,7 +283,7 @@ __global__ void plan_dense_kernel(int S, PlanOut po) {
     pdl_launch_dependents();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < S; i += gridDim.x * blockDim.x) po.slot[i] = i;
     if (blockIdx.x == 0 && threadIdx.x == 0) {
-        const int items = ((S + MMID_MAXTOK - 1) / MMID_MAXTOK) * po.nrt_gu;
+        const int items = ((S + po.mt_gu - 1) / po.mt_gu) * po.nrt_gu;
         po.active[0] = 0;
         po.aoffs[0] = 0; po.antok[0] = S;
         po.offs[0] = 0; po.offs[1] = S;
@@ -295,7 +295,7 @@ __global__ void plan_dense_kernel(int S, PlanOut po) {
 
 int launch_plan_dense(int S, const PlanBuffers &plan, int nrt, cudaStream_t st) {
     PlanOut po{plan.hdr, plan.active, plan.offs, plan.slot, plan.item_offs_gu, plan.item_offs_dn, nullptr,
-               plan.aoffs, plan.antok, nrt, nrt};
+               plan.aoffs, plan.antok, nrt, nrt, nullptr, plan.mt_gu, plan.mt_dn};
     const int grid = (S + 255) / 256 < 64 ? (S + 255) / 256 : 64;
     return launch_pdl(plan_dense_kernel, dim3(grid > 0 ? grid : 1), dim3(256), 0, st, S, po) == cudaSuccess
                ? ZMOE_OK
@@ -451,6 +451,33 @@ __global__ void __launch_bounds__(128) block_isums_kernel(const uint8_t *w, cons
         isum[(size_t)r * nb + b] = acc[b];
         msum[(size_t)r * nb + b] = acc[nb + b];
     }
+}
+
+// ------------------------------------------------------------------------
+// scalar gate of a shared expert: sigmoid(W_gi . x) per token (reference
+// models/graph/ggml_moe_graph_builder.cpp:120-124), one warp per token
+// ------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) token_gate_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                                                         float *__restrict__ g, int T, int D) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)t * D), *wr = reinterpret_cast<const float4 *>(w);
+    float s = 0.f;
+    for (int i = lane; i < D / 4; i += 32) {
+        const float4 a = xr[i], b = __ldg(wr + i);
+        s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (lane == 0) g[t] = 1.0f / (1.0f + expf(-s));
+}
+
+int launch_token_gate(const float *x, const float *w, float *g, int T, int D, cudaStream_t st) {
+    if (D % 4 || (reinterpret_cast<size_t>(x) & 15) || (reinterpret_cast<size_t>(w) & 15)) return ZMOE_ERR_ALIGN;
+    return launch_pdl(token_gate_kernel, dim3((T + 3) / 4), dim3(128), 0, st, x, w, g, T, D) == cudaSuccess ? ZMOE_OK
+                                                                                                            : ZMOE_ERR_CUDA;
 }
 
 int launch_block_isums(int type, const void *w, const uint8_t *q8, int32_t *isum, int32_t *msum, int rows, int I,

@@ -16,7 +16,7 @@ static bool mmid2_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
     const int bb = block_bytes(type), nb = I / QK_K, rb = nb * bb;
     if (nb < 2 || rb % 4 != 0) return false;
     const int ntile = dual ? 2 : 1;
-    const int budget = 200 * 1024;
+    const int budget = 208 * 1024;   // with the kernel's static arrays (about 15 KB) under the 227 KB a CTA may hold
     int cands[5], nc = 0;
     if (rb % 16 == 0) {
         cands[nc++] = dual ? 4 : 8;
@@ -44,9 +44,16 @@ static bool mmid2_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
         int q8s_l = q8row_stride(I_l);
         while ((q8s_l / 4) % 16 == 0) q8s_l += 16;
         const int wtile = (M2_R * pitch + 32 + 127) & ~127;
-        const int stage = (ntile * wtile + MMID_MAXTOK * q8s_l + 127) & ~127;
+        // eight pairs per item where the tensor-core consumer path serves the type (its cost does not depend on
+        // the pairs) and the wider activation area still fits; else four
+        int maxtok = (type == Q2_K || type == Q3_K || type == Q4_K) ? M2_MAXTOK : 4;
+        int stage = (ntile * wtile + maxtok * q8s_l + 127) & ~127;
+        while (maxtok > 4 && (size_t)stage * M2_NSET * M2_NSTG > (size_t)budget) {
+            --maxtok;
+            stage = (ntile * wtile + maxtok * q8s_l + 127) & ~127;
+        }
         if ((size_t)stage * M2_NSET * M2_NSTG > (size_t)budget) continue;
-        g->v2 = 1; g->cb = cb; g->acb = acb; g->nch = nb / cb; g->pitch = pitch; g->tiled = tiled ? 1 : 0;
+        g->v2 = 1; g->maxtok = maxtok; g->cb = cb; g->acb = acb; g->nch = nb / cb; g->pitch = pitch; g->tiled = tiled ? 1 : 0;
         g->lb_log2 = cb * 4 > 16 ? 3 : 2;   // up to four units per lane
         g->q8s_l = q8s_l;
         g->R = M2_R; g->wtile_bytes = wtile; g->stage_bytes = stage; g->nstage = M2_NSTG;
@@ -179,7 +186,7 @@ static int launch_mmid2(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st)
     if (!fn) return ZMOE_ERR_TYPE;
     if ((reinterpret_cast<size_t>(L.w0) & 15) || (L.dual && (reinterpret_cast<size_t>(L.w1) & 15))) return ZMOE_ERR_ALIGN;
     if (g.tiled && (!L.tm0 || (L.dual && !L.tm1))) return ZMOE_ERR_ARG;
-    if (raise_dynamic_smem(reinterpret_cast<const void *>(fn), 200 * 1024) != ZMOE_OK) return ZMOE_ERR_CUDA;
+    if (raise_dynamic_smem(reinterpret_cast<const void *>(fn), 208 * 1024) != ZMOE_OK) return ZMOE_ERR_CUDA;
     M2Params p;
     p.w0 = static_cast<const uint8_t *>(L.w0);
     p.w1 = static_cast<const uint8_t *>(L.w1);
@@ -189,6 +196,7 @@ static int launch_mmid2(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st)
     p.rb = (L.I / QK_K) * block_bytes(L.type);
     p.cb = g.cb; p.nch = g.nch; p.cbytes = g.cb * block_bytes(L.type);
     p.acb = g.acb;
+    p.maxtok = g.maxtok;
     p.pitch = g.pitch; p.lb_log2 = g.lb_log2; p.I_l = g.acb * QK_K; p.q8s_l = g.q8s_l; p.tiled = g.tiled;
     if (g.tiled) {
         p.tm0 = *L.tm0;

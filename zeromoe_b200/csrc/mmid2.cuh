@@ -5,7 +5,7 @@
 // kernels/quant/kquant_matmul.cu:647-700), restructured around what limited that kernel: every consumer warp
 // paid the fixed cost of a pipeline stage (barrier wait, descriptor, activation reload, reduction) for one or
 // two rows' worth of work.
-//   * An item is (expert, 32 consecutive rows, <= MMID_MAXTOK pairs).  It is streamed as chunks of CB
+//   * An item is (expert, 32 consecutive rows, up to 4 or 8 pairs).  It is streamed as chunks of CB
 //     super-blocks of all 32 rows: a stage holds [32 rows x CB blocks] of the tile (two tiles in DUAL mode)
 //     and the matching slice of the pairs' packed activation rows.  Where the tensor's rows are multiples of
 //     16 bytes the chunk is one tiled copy (box = chunk width x 32 rows); short rows of any length that is a
@@ -29,6 +29,7 @@ constexpr int M2_WPS = 4;              // warps per set
 constexpr int M2_NSTG = 2;             // stages per set
 constexpr int M2_NCW = M2_NSET * M2_WPS;
 constexpr int M2_R = 32;               // rows per item
+constexpr int M2_MAXTOK = 8;           // most pairs per item (the launch's maxtok is 4 or 8)
 
 struct M2Params {
     const uint8_t *w0, *w1;
@@ -42,6 +43,7 @@ struct M2Params {
     int acb;         // super-blocks of the activation slice a stage holds: cb, or 4 where cb is 2 (a slice
                      // must be copyable in 16-byte pieces; the slice then serves two consecutive chunks)
     int I_l;         // elements of that slice
+    int maxtok;      // pairs per item the plan was built with
     int q8s_l;       // bytes between the pairs' activation slices in shared memory
     int tiled;       // chunks come through tm0 / tm1
     const uint8_t *q8;
@@ -73,8 +75,7 @@ struct M2Meta {
     int expert, r0, nrows, ntok;
     int chunk, flags;          // flags: 1 = last chunk of the item, 2 = no more items for this set
     int w0_off, w1_off;
-    int pair[MMID_MAXTOK];
-    int pad[4];
+    int pair[M2_MAXTOK];
 };
 static_assert(sizeof(M2Meta) == 64, "meta");
 
@@ -175,8 +176,8 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
             it.e = e;
             it.r0 = rt * M2_R;
             it.nrows = min(M2_R, p.O - it.r0);
-            it.ntok = min(MMID_MAXTOK, ecnt - tc * MMID_MAXTOK);
-            it.pair = lane < it.ntok ? p.plan.slot[ebase + tc * MMID_MAXTOK + lane] : 0;
+            it.ntok = min(p.maxtok, ecnt - tc * p.maxtok);
+            it.pair = lane < it.ntok ? p.plan.slot[ebase + tc * p.maxtok + lane] : 0;
             return true;
         };
         Item cur, nxt;
@@ -267,7 +268,9 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
         const int np = M2_R / (M2_WPS * rpp);   // passes over the tile: 1 (four lanes per row) or 2 (eight)
         const int n_units = 4 * p.cb, upl = (n_units + LB - 1) >> p.lb_log2;
         const int cpa = p.acb / p.cb;
-        float acc[2][2][MMID_MAXTOK];           // [pass][matrix][pair]
+        // [pass][matrix][pair]; builds with the tensor-core path send every item of two or more pairs there
+        constexpr int SC = MMA ? 1 : M2_MAXTOK;
+        float acc[2][2][SC];
         float f0[4] = {0.f, 0.f, 0.f, 0.f};     // tensor-core path: (row g | g+8) x (pair 2c | 2c+1)
         // tensor-core path: warp = (16-row piece, matrix) in DUAL mode, (piece, half of the chunk) otherwise
         const int piece = ws >> 1, half = ws & 1;
@@ -306,18 +309,19 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
 #pragma unroll
                     for (int b = 0; b < 2; ++b)
 #pragma unroll
-                        for (int t = 0; t < MMID_MAXTOK; ++t) acc[a][b][t] = 0.f;
+                        for (int t = 0; t < SC; ++t) acc[a][b][t] = 0.f;
             }
             if (mma_item) {
                 // block b of the activation slice meets block b - ab of the chunk: shift the tile instead of the index
                 if (piece * 16 < m_nrows && hb0 < hb1)
-                    mma_rows<TYPE, false>((DUAL && half ? t1 : t0) + (uint32_t)(piece * 16) * p.pitch - (uint32_t)(ab * BB), 0, p.pitch,
-                                          q8base, p.q8s_l, p.I_l, hb0 + 2 * ab, hb1 + 2 * ab, lane, f0, f0);
+                    mma_rows<TYPE, false, false, M2_MAXTOK>((DUAL && half ? t1 : t0) + (uint32_t)(piece * 16) * p.pitch - (uint32_t)(ab * BB),
+                                                            0, p.pitch, q8base, p.q8s_l, p.I_l, hb0 + 2 * ab, hb1 + 2 * ab, lane, f0, f0, nullptr,
+                                                            p.maxtok - 1);
             } else if (TYPE == Q2_K && upl == 4) {
                 // a lane's four units are one super-block: the block-at-a-time form
                 if (bl < p.cb) {
 #pragma unroll
-                    for (int tk = 0; tk < MMID_MAXTOK; ++tk) {
+                    for (int tk = 0; tk < SC; ++tk) {
                         if (tk < m_ntok) {
 #pragma unroll
                             for (int pp = 0; pp < 2; ++pp) {
@@ -341,7 +345,7 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
                 }
             } else {
 #pragma unroll
-                for (int tk = 0; tk < MMID_MAXTOK; ++tk) {
+                for (int tk = 0; tk < SC; ++tk) {
                     if (tk < m_ntok) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -411,7 +415,7 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
                         if (pp < np) {
                             const int row = pp * M2_WPS * rpp + ws * rpp + rl;
 #pragma unroll
-                            for (int tk = 0; tk < MMID_MAXTOK; ++tk) {
+                            for (int tk = 0; tk < SC; ++tk) {
                                 if (tk < m_ntok) {
                                     float a0 = acc[pp][0][tk], a1 = DUAL ? acc[pp][1][tk] : 0.f;
                                     for (int off = LB >> 1; off > 0; off >>= 1) {

@@ -262,16 +262,20 @@ template <> struct MmaPath<Q4_K> { static constexpr bool kHas = true; static con
 // DBG (the parity hook of the integer stage): the per-super-block s32 sums of tile0 are also written to
 // dbg[((row * MMA_NTOK + pair) * (I / 256) + block) * 2 + {0: scale-weighted sum, 1: min-weighted sum}]; the range
 // [hb0, hb1) must then cover whole super-blocks.
-template <int TYPE, bool DUAL, bool DBG = false>
+// NT: pair columns the fragments are laid out for, 4 or 8; column g reads activation row min(g & (NT - 1), maxrow)
+// (maxrow + 1 = the rows the stage holds).  Columns past the item's pairs read whatever those rows hold and their
+// sums are never stored.
+template <int TYPE, bool DUAL, bool DBG = false, int NT = MMA_NTOK>
 __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb, uint32_t q8rows, int q8_stride, int I,
-                                         int hb0, int hb1, int lane, float (&f0)[4], float (&f1)[4], int *dbg = nullptr) {
+                                         int hb0, int hb1, int lane, float (&f0)[4], float (&f1)[4], int *dbg = nullptr,
+                                         int maxrow = NT - 1) {
     auto dbg_put = [&](int b, const int (&is)[4], const int (&ms)[4]) {
         const int g_ = lane >> 2, c_ = lane & 3;
-        if (2 * c_ < MMA_NTOK) {
+        if (2 * c_ < NT) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int row = g_ + 8 * (i >> 1), pair = 2 * c_ + (i & 1);
-                int *o = dbg + ((size_t)(row * MMA_NTOK + pair) * (I / 256) + b) * 2;
+                int *o = dbg + ((size_t)(row * NT + pair) * (I / 256) + b) * 2;
                 o[0] = is[i];
                 o[1] = ms[i];
             }
@@ -280,8 +284,9 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
     constexpr int BB = QTraits<TYPE>::kBytes;
     const int g = lane >> 2, c = lane & 3;
     const uint32_t offA = (uint32_t)g * rb, offB = (uint32_t)(g + 8) * rb;
-    const uint32_t qrow = q8rows + (uint32_t)(g & (MMA_NTOK - 1)) * q8_stride;   // column g's activations
-    const uint32_t drow = q8rows + (uint32_t)((2 * c) & (MMA_NTOK - 1)) * q8_stride + (uint32_t)q8row_d_off(I);
+    const uint32_t qrow = q8rows + (uint32_t)min(g & (NT - 1), maxrow) * q8_stride;   // column g's activations
+    const uint32_t drow = q8rows + (uint32_t)min((2 * c) & (NT - 1), maxrow) * q8_stride + (uint32_t)q8row_d_off(I);
+    const uint32_t drow1 = q8rows + (uint32_t)min(((2 * c) & (NT - 1)) + 1, maxrow) * q8_stride + (uint32_t)q8row_d_off(I);
     const uint32_t bs_off = (uint32_t)q8row_bs_off(I) + 8 * c;
     if (TYPE == Q2_K) {
         for (int b = hb0 >> 1; b < (hb1 >> 1); ++b) {
@@ -290,7 +295,7 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
                 const uint2 w = lds64(qrow + bs_off + 32 * b);
                 bsum_planes(w.x, w.y, bs_hi, bs_lo);
             }
-            const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow + q8_stride + 4 * b));
+            const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow1 + 4 * b));
             const uint32_t qblk = qrow + (uint32_t)(4 * b) * Q8_UNIT_STRIDE + 4 * c;
             const uint32_t boff = (uint32_t)b * BB;
             int cm0[4], cm1[4];
@@ -323,7 +328,7 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
             // group sums of sub-blocks 4c'..4c'+3, c' = c & 1; lanes with c >= 2 multiply them by zero mins
             uint32_t bs_hi, bs_lo;
             bsum_pair_planes(lds128(qrow + (uint32_t)q8row_bs_off(I) + 32 * b + 16 * (c & 1)), bs_hi, bs_lo);
-            const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow + q8_stride + 4 * b));
+            const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow1 + 4 * b));
             const uint32_t qblk = qrow + (uint32_t)(4 * b) * Q8_UNIT_STRIDE + 4 * c;
             const uint32_t boff = (uint32_t)b * BB;
 #pragma unroll
@@ -383,7 +388,7 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
             }
             if ((hb & 1) == 1 || hb + 1 == hb1) {
                 // the super-block (or this warp's share of it) is complete: scale into f32
-                const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow + q8_stride + 4 * b));
+                const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow1 + 4 * b));
 #pragma unroll
                 for (int m = 0; m < (DUAL ? 2 : 1); ++m) {
                     const uint32_t t = m ? tile1 : tile0;

@@ -36,6 +36,7 @@ struct PlanOut {
     int *antok;        // [E] pairs of active[a]
     int nrt_gu, nrt_dn;  // row tiles per expert of the two projections
     int *pos = nullptr;  // [P] inverse of slot: position of pair p in expert order, -1 for an inactive route; may be null
+    int mt_gu = 4, mt_dn = 4;  // pairs per item of the two projections
 };
 
 __device__ __forceinline__ float gate_scalar(float x, int gating) {
@@ -175,8 +176,9 @@ __device__ void build_plan_cta(const int32_t *ids, int P, int E, const PlanOut &
             const int c = cnt_s[e];
             cs += c;
             if (c > 0) {
-                const int ntc = (c + MMID_MAXTOK - 1) / MMID_MAXTOK;
-                ++as; gs += ntc * po.nrt_gu; ds += ntc * po.nrt_dn;
+                ++as;
+                gs += ((c + po.mt_gu - 1) / po.mt_gu) * po.nrt_gu;
+                ds += ((c + po.mt_dn - 1) / po.mt_dn) * po.nrt_dn;
             }
         }
         int xs[4] = {cs, as, gs, ds}, tot[4];
@@ -198,12 +200,11 @@ __device__ void build_plan_cta(const int32_t *ids, int P, int E, const PlanOut &
             po.offs[e] = run;
             if (po.freq) po.freq[e] = c;
             if (c > 0) {
-                const int ntc = (c + MMID_MAXTOK - 1) / MMID_MAXTOK;
                 po.active[na] = e;
                 po.aoffs[na] = run;
                 po.antok[na] = c;
-                igu += ntc * po.nrt_gu;
-                idn += ntc * po.nrt_dn;
+                igu += ((c + po.mt_gu - 1) / po.mt_gu) * po.nrt_gu;
+                idn += ((c + po.mt_dn - 1) / po.mt_dn) * po.nrt_dn;
                 ++na;
                 po.item_offs_gu[na] = igu;
                 po.item_offs_dn[na] = idn;

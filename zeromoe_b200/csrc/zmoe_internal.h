@@ -38,6 +38,7 @@ struct PlanBuffers {
     int *aoffs = nullptr, *antok = nullptr;
     int *pos = nullptr;    // [P] position of each pair in expert order (inverse of slot), -1 = inactive; optional
     int cap_e = 0;
+    int mt_gu = 4, mt_dn = 4;   // pairs per item of the two projections (the geometry's maxtok)
 };
 
 constexpr int ROUTER_MAX_GROUPS = 64;   // token groups (of 4) the decode router can ticket: 256 tokens
@@ -78,6 +79,7 @@ struct MmidGeom {
     int pitch = 0;         // bytes between rows of a chunk in shared memory
     int lb_log2 = 0;       // log2 of the lanes that share a row on the one-pair path
     int q8s_l = 0;         // bytes between the pairs' activation slices in shared memory
+    int maxtok = 4;        // pairs per item (8 where the K-chunked kernel has the tensor-core path and the stages fit)
     int tiled = 0;         // chunks come through tiled maps (make_chunk_map); 0: rows are copied whole as one run
 };
 // allow_v2: the caller passes maps made by make_chunk_map where g->tiled is set
@@ -110,6 +112,8 @@ struct MmidLaunch {
 // Map of a [E][O rows][rb bytes] weight tensor whose box is R rows of rb + 16 bytes: the 16 bytes past the
 // end of a row are out of bounds and arrive as zeros, which pads the rows in shared memory.  Rows up to 2032 bytes.
 int make_rows_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t expert_stride, int R);
+// g[t] = sigmoid(w . x[t]) for T rows of D floats (D a multiple of 4)
+int launch_token_gate(const float *x, const float *w, float *g, int T, int D, cudaStream_t st);
 int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st);
 // s32 sums of the tensor-core consumer path: out[16 rows][4 pair slots][I / 256][2]
 int launch_mma_isums(int type, const void *w, const uint8_t *q8, int *out, int I, int pairs, cudaStream_t st);

@@ -22,7 +22,7 @@ EXPORTS = [
     "launch_expert_scatter_add", "launch_glm5next_router_topk", "zmoe_matmul_noalloc", "zmoe_reserve", "zmoe_last_status",
     "zmoe_f32_quant_hook", "zeromoe_install_f32_quant_graph_hook", "zeromoe_f32_quant_graph_launches",
     "zmoe_ctx_create", "zmoe_ctx_destroy", "zmoe_layer_create", "zmoe_layer_destroy", "zmoe_route",
-    "zmoe_set_routes", "zmoe_set_routes_strided", "zmoe_set_routes_window", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_dense_ffn", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
+    "zmoe_set_routes", "zmoe_set_routes_strided", "zmoe_set_routes_window", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_dense_ffn", "zmoe_dense_ffn_gated", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
     "zmoe_get_expert_freq", "zmoe_copy_routes", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_set_path", "zmoe_ctx_check", "zmoe_kernel_launches",
     "zmoe_quantize_q8_K", "zmoe_block_isums", "zmoe_block_isums_pairs",
     "zmoe_device_status", "zmoe_selftest_wait_expiry", "zmoe_ctx_bad_counts", "zmoe_gemm_min_pairs_per_expert",
@@ -122,6 +122,7 @@ def load():
     L.zmoe_expert_ffn.argtypes = [vp, vp, i, i, vp]
     L.zmoe_expert_ffn_events.argtypes = [vp, vp, i, i, vp, vp, vp]
     L.zmoe_dense_ffn.argtypes = [vp, vp, vp, i, i, vp]
+    L.zmoe_dense_ffn_gated.argtypes = [vp, vp, vp, vp, i, i, vp]
     L.zmoe_moe_forward.argtypes = [vp, vp, vp, i, vp]
     L.zmoe_moe_forward_host.argtypes = [vp, vp, vp, i]
     L.zmoe_get_routes.argtypes = [vp, i, i, vp, vp]
@@ -303,6 +304,11 @@ class Layer:
         """single-expert layer applied to every token (shared expert)"""
         check(load().zmoe_dense_ffn(self.h, ptr(x), ptr(out), x.shape[0], accumulate, _stream_ptr(stream)),
               "zmoe_dense_ffn")
+
+    def dense_ffn_gated(self, x, gate_w, out, accumulate=0, stream=None):
+        """dense_ffn with every token's row scaled by sigmoid(gate_w . x[t])"""
+        check(load().zmoe_dense_ffn_gated(self.h, ptr(x), ptr(gate_w), ptr(out), x.shape[0], accumulate, _stream_ptr(stream)),
+              "zmoe_dense_ffn_gated")
 
     def forward(self, x, out, stream=None):
         check(load().zmoe_moe_forward(self.h, ptr(x), ptr(out), x.shape[0], _stream_ptr(stream)), "zmoe_moe_forward")
