@@ -781,15 +781,15 @@ def main():
                 gu_ms += sum(a.elapsed_time(b) for a, b in evs)
         gu_ms /= reps * LAYERS
         ach = (sum(gu_bytes) / LAYERS) / (gu_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "mmid_kernel<Q2_K, dual> (gate/up matmul + SwiGLU)", "achieved": ach,
+        roofline = {"bound": "hbm", "kernel": "mmid2_kernel<Q2_K, dual> (gate/up matmul + SwiGLU)", "achieved": ach,
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_source": which,
                     "avg_launch_ms": gu_ms, "bytes_per_launch": sum(gu_bytes) / LAYERS,
                     # dram__bytes_read + write of this kernel from ncu on a 1-layer capture of the same
-                    # batch: 357.8 MB for 351.0 MB of algorithmic bytes; traffic is proportional to the
-                    # distinct experts streamed, so the ratio carries over to a full launch
-                    "traffic": sum(gu_bytes) / LAYERS * (357.82 / 351.0),
+                    # batch: 343.0 MB read + 5.3 MB written for 342.8 MB of algorithmic bytes; traffic is
+                    # proportional to the distinct experts streamed, so the ratio carries over to a full launch
+                    "traffic": sum(gu_bytes) / LAYERS * (348.25 / 342.8),
                     "traffic_source": "scaled from the ncu capture of a 1-layer run of the same batch "
-                                      "(profiles/mmid_kernel_decode_cfg2.md), not measured in this run",
+                                      "(profiles/mmid2_kernel_decode_cfg2.md), not measured in this run",
                     "distinct_experts_per_layer": nact}
         step_bytes = sum(gu_bytes) + sum(dn_bytes) + LAYERS * E * D * 4
         layer_roofline = {"algorithmic_bytes_per_step": step_bytes, "achieved": step_bytes / (ms_step * 1e-3) / 1e9,
