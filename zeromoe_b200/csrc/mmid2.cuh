@@ -5,18 +5,21 @@
 // kernels/quant/kquant_matmul.cu:647-700), restructured around what limited that kernel: every consumer warp
 // paid the fixed cost of a pipeline stage (barrier wait, descriptor, activation reload, reduction) for one or
 // two rows' worth of work.
-//   * An item is (expert, 32 consecutive rows, up to 4 or 8 pairs).  It is streamed as chunks of CB
-//     super-blocks of all 32 rows: a stage holds [32 rows x CB blocks] of the tile (two tiles in DUAL mode)
-//     and the matching slice of the pairs' packed activation rows.  Where the tensor's rows are multiples of
-//     16 bytes the chunk is one tiled copy (box = chunk width x 32 rows); short rows of any length that is a
-//     multiple of 4 bytes are copied whole (one chunk) as a contiguous run.
-//   * The 12 consumer warps form three sets of four.  Each set has its own ring of two stages and works on
-//     its own item: a warp's share of a stage is 8 rows x CB blocks (x 2 matrices), accumulated in registers
-//     across the item's chunks, so the per-stage fixed cost is spread over 8 to 16 times more arithmetic and no
-//     reduction runs until the item ends.  The producer warp hands the next item to whichever set is free.
-//   * One pair per item: a lane owns one super-block of one row (and of its partner row in the other matrix).
-//     Two or more pairs: mma.sync on 16-row pieces (mmid_mma.cuh); the set's warps split pieces and matrices
-//     (DUAL) or pieces and halves of the chunk, and meet through shared memory once per item.
+//   * An item is (expert, 32 consecutive rows, up to `maxtok` pairs: 4 to 8, what the stages have room for).  It is
+//     streamed as chunks of CB super-blocks of all 32 rows: a stage holds [32 rows x CB blocks] of the tile (two
+//     tiles in DUAL mode) and the matching slice of the pairs' packed activation rows.  Where the tensor's rows
+//     are multiples of 16 bytes the chunk is one tiled copy (box = chunk width x 32 rows); short rows of any
+//     length that is a multiple of 4 bytes are copied whole (one chunk) as a contiguous run.
+//   * The 12 consumer warps form three sets of four.  Each set has its own ring of two stages, its own producer
+//     warp and works on its own item: a warp's share of a stage is 8 rows x CB blocks (x 2 matrices),
+//     accumulated in registers across the item's chunks, so the per-stage fixed cost is spread over 8 to 16
+//     times more arithmetic and no reduction runs until the item ends.  A producer takes the CTA's next item
+//     from a shared counter, so sets with light items simply take more of them.  (One producer warp for all
+//     three sets was measured to be the bottleneck: it shares a scheduler with three busy consumer warps.)
+//   * One pair per item: a lane owns a run of units of one row (and of its partner row in the other matrix);
+//     Q2_K decodes a super-block at a time.  Two or more pairs: mma.sync on 16-row pieces (mmid_mma.cuh) with all
+//     eight fragment columns in use; the set's warps split pieces and matrices (DUAL) or pieces and halves of
+//     the chunk, and meet through shared memory once per item.
 // Every wait is bounded; on expiry the warp raises the error flag and leaves.
 #pragma once
 
