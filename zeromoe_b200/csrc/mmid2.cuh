@@ -273,6 +273,7 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
         const int cpa = p.acb / p.cb;
         // [pass][matrix][pair]; builds with the tensor-core path send every item of two or more pairs there
         constexpr int SC = MMA ? 1 : M2_MAXTOK;
+        constexpr int UNIT_UNROLL = (TYPE == Q3_K || TYPE == IQ2_XXS) ? 1 : 4;
         float acc[2][2][SC];
         float f0[4] = {0.f, 0.f, 0.f, 0.f};     // tensor-core path: (row g | g+8) x (pair 2c | 2c+1)
         // tensor-core path: warp = (16-row piece, matrix) in DUAL mode, (piece, half of the chunk) otherwise
@@ -350,10 +351,12 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
 #pragma unroll
                 for (int tk = 0; tk < SC; ++tk) {
                     if (tk < m_ntok) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
+                        // the unit loop stays rolled for the formats whose unit dot is long (Q3_K, IQ2_XXS): unrolled, the
+                        // consumer loop outgrew the instruction cache (84 % hit rate, "no instruction" the top stall)
+#pragma unroll(UNIT_UNROLL)
+                        for (int i = 0; i < upl; ++i) {
                             const int u = bl * upl + i;
-                            if (i >= upl || u >= n_units) continue;
+                            if (u >= n_units) continue;
                             const int sub = u & 3;
                             const uint32_t boff = (uint32_t)(u >> 2) * BB;
                             UnitAct ua;

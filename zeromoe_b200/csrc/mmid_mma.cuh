@@ -138,12 +138,15 @@ __device__ __forceinline__ void q2k_mins(uint32_t rowA, uint32_t rowB, int c, ui
 // -4 * sum over groups of scale * (group sum of the activations): k16 instructions with the signed scales
 // as A bytes, masked to this half's groups.
 // rowA / rowB: the block in rows g and g+8; N: which half; acc: scaled integer sums of the super-block.
-template <bool MIS, int N>
-__device__ __forceinline__ void q3k_half(uint32_t rowA, uint32_t rowB, int c, const uint32_t (&bq)[4][2],
+// N (which half) is a run-time value: one copy of this code per alignment instead of two keeps the consumer loop
+// inside the instruction cache.
+template <bool MIS>
+__device__ __forceinline__ void q3k_half(uint32_t rowA, uint32_t rowB, int c, int N, const uint32_t (&bq)[4][2],
                                          uint32_t bs_hi, uint32_t bs_lo, int (&acc)[4]) {
     const uint32_t qA = rowA + 4 * c, qB = rowB + 4 * c;
-    const uint32_t qa[2] = {ldso_mis<MIS, 32 + 32 * N>(qA), ldso_mis<MIS, 48 + 32 * N>(qA)};
-    const uint32_t qb[2] = {ldso_mis<MIS, 32 + 32 * N>(qB), ldso_mis<MIS, 48 + 32 * N>(qB)};
+    const uint32_t qAn = qA + 32 * N, qBn = qB + 32 * N;
+    const uint32_t qa[2] = {ldso_mis<MIS, 32>(qAn), ldso_mis<MIS, 48>(qAn)};
+    const uint32_t qb[2] = {ldso_mis<MIS, 32>(qBn), ldso_mis<MIS, 48>(qBn)};
     // plane bit of shift s of this half is bit 4n + s of the mask byte: bring bit 4n to bit 0
     const uint32_t ha[2] = {ldso_mis<MIS, 0>(qA) >> (4 * N), ldso_mis<MIS, 16>(qA) >> (4 * N)};
     const uint32_t hb[2] = {ldso_mis<MIS, 0>(qB) >> (4 * N), ldso_mis<MIS, 16>(qB) >> (4 * N)};
@@ -369,21 +372,14 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
             uint32_t bq[4][2];
             // blocks of 110 bytes: every other block starts 2 modulo 4, the same for all lanes
             const bool mis0 = (tile0 + boff) & 2u, mis1 = (tile1 + boff) & 2u;
-            if ((hb & 1) == 0) {
-                load_b_half<0>(qblk, bq);
-                if (mis0) q3k_half<true, 0>(tile0 + offA + boff, tile0 + offB + boff, c, bq, bs_hi, bs_lo, a0);
-                else q3k_half<false, 0>(tile0 + offA + boff, tile0 + offB + boff, c, bq, bs_hi, bs_lo, a0);
+            {
+                const int nh = hb & 1;
+                load_b_half<0>(qblk + (uint32_t)(2 * nh) * Q8_UNIT_STRIDE, bq);
+                if (mis0) q3k_half<true>(tile0 + offA + boff, tile0 + offB + boff, c, nh, bq, bs_hi, bs_lo, a0);
+                else q3k_half<false>(tile0 + offA + boff, tile0 + offB + boff, c, nh, bq, bs_hi, bs_lo, a0);
                 if (DUAL) {
-                    if (mis1) q3k_half<true, 0>(tile1 + offA + boff, tile1 + offB + boff, c, bq, bs_hi, bs_lo, a1);
-                    else q3k_half<false, 0>(tile1 + offA + boff, tile1 + offB + boff, c, bq, bs_hi, bs_lo, a1);
-                }
-            } else {
-                load_b_half<1>(qblk, bq);
-                if (mis0) q3k_half<true, 1>(tile0 + offA + boff, tile0 + offB + boff, c, bq, bs_hi, bs_lo, a0);
-                else q3k_half<false, 1>(tile0 + offA + boff, tile0 + offB + boff, c, bq, bs_hi, bs_lo, a0);
-                if (DUAL) {
-                    if (mis1) q3k_half<true, 1>(tile1 + offA + boff, tile1 + offB + boff, c, bq, bs_hi, bs_lo, a1);
-                    else q3k_half<false, 1>(tile1 + offA + boff, tile1 + offB + boff, c, bq, bs_hi, bs_lo, a1);
+                    if (mis1) q3k_half<true>(tile1 + offA + boff, tile1 + offB + boff, c, nh, bq, bs_hi, bs_lo, a1);
+                    else q3k_half<false>(tile1 + offA + boff, tile1 + offB + boff, c, nh, bq, bs_hi, bs_lo, a1);
                 }
             }
             if ((hb & 1) == 1 || hb + 1 == hb1) {
