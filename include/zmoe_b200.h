@@ -232,6 +232,10 @@ int zmoe_dense_ffn_gated(zmoe_layer *layer, const float *x_dev, const float *gat
                          int accumulate, void *stream);
 /* zmoe_route followed by zmoe_expert_ffn */
 int zmoe_moe_forward(zmoe_layer *layer, const float *x_dev, float *out_dev, int T, void *stream);
+/* the same for bf16 activations (x_bf16_dev [T, d_model], 16-byte aligned): the third benchmark configuration's
+ * input type.  The rows are widened (exactly) into the context's staging buffer, which zmoe_moe_forward_host also
+ * uses: one of the two at a time per context. */
+int zmoe_moe_forward_bf16(zmoe_layer *layer, const void *x_bf16_dev, float *out_dev, int T, void *stream);
 /* the same with host buffers: copies x in, runs the layer, copies out back, synchronises */
 int zmoe_moe_forward_host(zmoe_layer *layer, const float *x_host, float *out_host, int T);
 

@@ -62,6 +62,50 @@ static bool check_matmul(GGUFType type, int I, int O, int S) {
     return true;
 }
 
+// one expert through the issue / finish triple, slab = [gate | up | down], host input and host output, against the
+// oracle's layer with that one expert
+static bool check_triple() {
+    std::mt19937 rng(7);
+    const int D = 512, F = 256, S = 3;
+    const int tg = ZO_TYPE_Q2_K, td = ZO_TYPE_Q3_K;
+    auto wg = random_blocks(tg, (size_t)F * (D / 256), rng), wu = random_blocks(tg, (size_t)F * (D / 256), rng);
+    auto wd = random_blocks(td, (size_t)D * (F / 256), rng);
+    std::vector<uint8_t> slab;
+    slab.insert(slab.end(), wg.begin(), wg.end());
+    slab.insert(slab.end(), wu.begin(), wu.end());
+    slab.insert(slab.end(), wd.begin(), wd.end());
+    std::normal_distribution<float> nd(0.f, 1.f);
+    std::vector<float> x((size_t)S * D), ref((size_t)S * D), got((size_t)S * D);
+    for (auto &v : x) v = nd(rng);
+    std::vector<int32_t> ids(S, 0);
+    std::vector<float> w(S, 1.0f);
+    zo_layer L = {D, F, 1, 1, tg, tg, td, wg.data(), wu.data(), wd.data(), wg.size(), wu.size(), wd.size(), 0.0f, 0};
+    zo_moe_ffn(&L, x.data(), ids.data(), w.data(), S, ref.data(), nullptr);
+    uint8_t *dslab = nullptr;
+    cudaMalloc(&dslab, slab.size() + 64);
+    cudaMemcpy(dslab, slab.data(), slab.size(), cudaMemcpyHostToDevice);
+    ExpertLocation loc;
+    loc.gpu_id = 0; loc.device_ptr = dslab; loc.size = slab.size(); loc.layer_idx = 0; loc.expert_id = 0;
+    const GGUFTensor gate_meta{GGUFType::Q2_K, 1000}, up_meta{GGUFType::Q2_K, 1000 + wg.size()},
+        down_meta{GGUFType::Q3_K, 1000 + wg.size() + wu.size()};   // offsets inside the file-side slab; only differences count
+    GpuTopology topo;
+    GpuExpertScratch scratch;
+    bool ok = expert_ffn_gpu_issue(scratch, &loc, x.data(), gate_meta, up_meta, S, D, F, &topo);
+    if (ok) {
+        expert_ffn_gpu_finish_stage1(scratch, &loc, nullptr, nullptr, gate_meta, down_meta, 0, 0, S, D, F, 0.0f, &topo);
+        expert_ffn_gpu_finish_stage2(&loc, got.data(), 0, 0, S, D, &topo, true, false, scratch);
+    }
+    ok = ok && zmoe_last_status() == ZMOE_OK;
+    double m = 0, n = 0;
+    for (size_t i = 0; i < got.size(); ++i) { m = std::fmax(m, std::fabs((double)got[i] - ref[i])); n += (double)ref[i] * ref[i]; }
+    if (m / (std::sqrt(n) + 1e-30) > 1e-3) { std::printf("  triple error/norm %.3e\n", m / std::sqrt(n)); ok = false; }
+    // a missing location is an error, not a CPU fallback
+    ok = ok && !expert_ffn_gpu_issue(scratch, nullptr, x.data(), gate_meta, up_meta, S, D, F, &topo);
+    scratch.release();
+    cudaFree(dslab);
+    return ok;
+}
+
 int main() {
     int fails = 0;
     struct { GGUFType t; int I, O, S; const char *name; } cases[] = {
@@ -78,6 +122,11 @@ int main() {
     const bool refused = !CudaKernelDispatcher::matmul(GGUFType::Q8_0, nullptr, nullptr, nullptr, 1, 256, 1);
     std::printf("%s unsupported type refused\n", refused ? "PASS" : "FAIL");
     fails += !refused;
+    {
+        const bool ok = check_triple();
+        std::printf("%s per-expert issue / finish triple with the reference's argument lists\n", ok ? "PASS" : "FAIL");
+        fails += !ok;
+    }
     // a layer call with a null layer aborts instead of falling back
     MoePipelineContext ctx;
     const bool aborted = BatchedDispatchPipeline::run(ctx) == BatchedDispatchResult::Abort;

@@ -546,6 +546,37 @@ def test_shared_expert_with_scalar_gate(zlib, oracle, dev):
     assert zlib.load().zmoe_dense_ffn_gated(shared.h, None, zlib.ptr(out), zlib.ptr(out), T, 0, None) == -1
 
 
+@pytest.mark.parametrize("T", [3, 300])
+def test_moe_forward_bf16_activations(zlib, oracle, dev, T):
+    """bf16 activations (the third configuration's input type) give exactly what their f32 widening gives, on the
+    decode kernels (3 tokens) and on the tensor-core path (300 tokens, 75 pairs per expert)"""
+    import torch
+    D, F, E, K = 1024, 512, 16, 4
+    types = (synth.Q4_K,) * 3
+    rng = synth.rng_for(37, T)
+    wg = synth.expert_weights(types[0], E, F, D, rng)
+    wu = synth.expert_weights(types[1], E, F, D, rng)
+    wd = synth.expert_weights(types[2], E, D, F, rng)
+    wr = synth.router_weights(E, D, rng, sigma=0.05)
+    xb = torch.from_numpy(synth.activations(T, D, rng)).to(dev).to(torch.bfloat16)
+    xf = xb.to(torch.float32)
+    ctx = zlib.Context(512, D, F, E, K)
+    layer = zlib.Layer(ctx, D, F, E, K, types, to_dev(wg, dev), to_dev(wu, dev), to_dev(wd, dev), router_w=to_dev(wr, dev))
+    out_b = torch.zeros((T, D), device=dev)
+    out_f = torch.zeros((T, D), device=dev)
+    layer.forward(xf, out_f)
+    _sync()
+    ids_f, _ = ctx.routes(T, K)
+    layer.forward_bf16(xb, out_b)
+    _sync()
+    ctx.check()
+    ids_b, w_b = ctx.routes(T, K)
+    assert np.array_equal(ids_f, ids_b)
+    assert torch.equal(out_b, out_f)
+    ref = oracle.moe_ffn(oracle.make_layer(D, F, E, K, types, wg, wu, wd), xf.cpu().numpy(), ids_b, w_b, fast=True)[0]
+    assert rel_to_norm(out_b.cpu().numpy(), ref) < REL_TO_NORM
+
+
 def test_moe_forward_host_buffers(zlib, oracle, dev):
     import torch
     D, F, E, K, T = 1024, 512, 16, 4, 4

@@ -580,6 +580,17 @@ int zmoe_moe_forward(zmoe_layer *L, const float *x_dev, float *out_dev, int T, v
     return rc;
 }
 
+int zmoe_moe_forward_bf16(zmoe_layer *L, const void *x_bf16_dev, float *out_dev, int T, void *stream) {
+    if (!L || !x_bf16_dev || !out_dev || T <= 0) return ZMOE_ERR_ARG;
+    zmoe_ctx *c = L->ctx;
+    if (T > c->max_t) return ZMOE_ERR_CAPACITY;
+    // widened once into the context's staging rows (exact); router and matmuls then read f32 as ever
+    int rc = launch_widen_bf16(x_bf16_dev, c->x_stage, (long)T * L->d.d_model, c->n_sm, static_cast<cudaStream_t>(stream));
+    g_launches += 1;
+    if (!rc) rc = zmoe_moe_forward(L, c->x_stage, out_dev, T, stream);
+    return rc;
+}
+
 int zmoe_moe_forward_host(zmoe_layer *L, const float *x_host, float *out_host, int T) {
     if (!L || !x_host || !out_host || T <= 0) return ZMOE_ERR_ARG;
     zmoe_ctx *c = L->ctx;

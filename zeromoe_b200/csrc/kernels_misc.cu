@@ -480,6 +480,31 @@ int launch_token_gate(const float *x, const float *w, float *g, int T, int D, cu
                                                                                                             : ZMOE_ERR_CUDA;
 }
 
+// bf16 -> f32, eight values per thread per step (the widening is exact)
+__global__ void __launch_bounds__(256) widen_bf16_kernel(const uint4 *__restrict__ src, float4 *__restrict__ dst, long n8) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+        const uint4 v = src[i];
+        float4 a, b;
+        a.x = __uint_as_float(v.x << 16); a.y = __uint_as_float(v.x & 0xffff0000u);
+        a.z = __uint_as_float(v.y << 16); a.w = __uint_as_float(v.y & 0xffff0000u);
+        b.x = __uint_as_float(v.z << 16); b.y = __uint_as_float(v.z & 0xffff0000u);
+        b.z = __uint_as_float(v.w << 16); b.w = __uint_as_float(v.w & 0xffff0000u);
+        dst[2 * i] = a;
+        dst[2 * i + 1] = b;
+    }
+}
+
+int launch_widen_bf16(const void *src, float *dst, long n, int n_sm, cudaStream_t st) {
+    if (n % 8 || (reinterpret_cast<size_t>(src) & 15) || (reinterpret_cast<size_t>(dst) & 15)) return ZMOE_ERR_ALIGN;
+    const long n8 = n / 8;
+    long grid = (n8 + 255) / 256;
+    if (grid > 8L * n_sm) grid = 8L * n_sm;
+    return launch_pdl(widen_bf16_kernel, dim3((unsigned)(grid > 0 ? grid : 1)), dim3(256), 0, st, static_cast<const uint4 *>(src),
+                      reinterpret_cast<float4 *>(dst), n8) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
+}
+
 int launch_block_isums(int type, const void *w, const uint8_t *q8, int32_t *isum, int32_t *msum, int rows, int I,
                        cudaStream_t st) {
     if (rows <= 0) return ZMOE_OK;

@@ -112,6 +112,8 @@ struct MmidLaunch {
 // Map of a [E][O rows][rb bytes] weight tensor whose box is R rows of rb + 16 bytes: the 16 bytes past the
 // end of a row are out of bounds and arrive as zeros, which pads the rows in shared memory.  Rows up to 2032 bytes.
 int make_rows_map(CUtensorMap *m, const void *base, int E, int O, int rb, size_t expert_stride, int R);
+// dst[i] = (float)src[i] for n bf16 values (n a multiple of 8, both 16-byte aligned)
+int launch_widen_bf16(const void *src, float *dst, long n, int n_sm, cudaStream_t st);
 // g[t] = sigmoid(w . x[t]) for T rows of D floats (D a multiple of 4)
 int launch_token_gate(const float *x, const float *w, float *g, int T, int D, cudaStream_t st);
 int launch_mmid(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st);

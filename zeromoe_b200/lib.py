@@ -22,7 +22,7 @@ EXPORTS = [
     "launch_expert_scatter_add", "launch_glm5next_router_topk", "zmoe_matmul_noalloc", "zmoe_reserve", "zmoe_last_status",
     "zmoe_f32_quant_hook", "zeromoe_install_f32_quant_graph_hook", "zeromoe_f32_quant_graph_launches",
     "zmoe_ctx_create", "zmoe_ctx_destroy", "zmoe_layer_create", "zmoe_layer_destroy", "zmoe_route",
-    "zmoe_set_routes", "zmoe_set_routes_strided", "zmoe_set_routes_window", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_dense_ffn", "zmoe_dense_ffn_gated", "zmoe_moe_forward", "zmoe_moe_forward_host", "zmoe_get_routes",
+    "zmoe_set_routes", "zmoe_set_routes_strided", "zmoe_set_routes_window", "zmoe_expert_ffn", "zmoe_expert_ffn_events", "zmoe_dense_ffn", "zmoe_dense_ffn_gated", "zmoe_moe_forward", "zmoe_moe_forward_bf16", "zmoe_moe_forward_host", "zmoe_get_routes",
     "zmoe_get_expert_freq", "zmoe_copy_routes", "zmoe_get_probs", "zmoe_get_act", "zmoe_ctx_set_path", "zmoe_ctx_check", "zmoe_kernel_launches",
     "zmoe_quantize_q8_K", "zmoe_block_isums", "zmoe_block_isums_pairs",
     "zmoe_device_status", "zmoe_selftest_wait_expiry", "zmoe_ctx_bad_counts", "zmoe_gemm_min_pairs_per_expert",
@@ -123,6 +123,7 @@ def load():
     L.zmoe_expert_ffn_events.argtypes = [vp, vp, i, i, vp, vp, vp]
     L.zmoe_dense_ffn.argtypes = [vp, vp, vp, i, i, vp]
     L.zmoe_dense_ffn_gated.argtypes = [vp, vp, vp, vp, i, i, vp]
+    L.zmoe_moe_forward_bf16.argtypes = [vp, vp, vp, i, vp]
     L.zmoe_moe_forward.argtypes = [vp, vp, vp, i, vp]
     L.zmoe_moe_forward_host.argtypes = [vp, vp, vp, i]
     L.zmoe_get_routes.argtypes = [vp, i, i, vp, vp]
@@ -312,6 +313,11 @@ class Layer:
 
     def forward(self, x, out, stream=None):
         check(load().zmoe_moe_forward(self.h, ptr(x), ptr(out), x.shape[0], _stream_ptr(stream)), "zmoe_moe_forward")
+
+    def forward_bf16(self, x_bf16, out, stream=None):
+        """forward for a torch.bfloat16 activation tensor [T, d_model]"""
+        check(load().zmoe_moe_forward_bf16(self.h, ptr(x_bf16), ptr(out), x_bf16.shape[0], _stream_ptr(stream)),
+              "zmoe_moe_forward_bf16")
 
     def forward_host(self, x_host, out_host):
         """x_host / out_host: host tensors or arrays [T, d_model] f32 (pinned for full speed)"""
