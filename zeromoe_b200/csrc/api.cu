@@ -374,6 +374,7 @@ int zmoe_route(zmoe_layer *L, const float *x_dev, int T, void *stream) {
     a.logits = c->logits; a.ids = c->ids; a.weights = c->weights; a.q8x = c->q8x;
     a.q8_layout = q8_layout_of(L->d.gate.type);
     a.plan = c->plan.b;
+    a.stats = gemm_stats_buffer(0);
     c->plan_small = (long)T * L->d.topk <= kSmallCallPairs;
     const zmoe_layer::Proj &ps = c->plan_small ? L->small : L->big;
     a.plan.mt_gu = ps.mt_gu; a.plan.mt_dn = ps.mt_dn;

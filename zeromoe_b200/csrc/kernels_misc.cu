@@ -28,6 +28,11 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const Rou
     constexpr int NW = ROUTER_THREADS / 32;
     pdl_wait_prior_grid();
     pdl_launch_dependents();
+#ifdef ZMOE_GEMM_STATS
+    unsigned long long rt[6];
+    auto now = []() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+    rt[0] = now();
+#endif
 
     const int e = blockIdx.x % a.E, tg = blockIdx.x / a.E;
     const int t0 = tg * ROUTER_TPB;
@@ -81,12 +86,18 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const Rou
     }
     // Two levels of tickets: the last of the E CTAs of a token group routes that group's tokens (one warp per
     // token) while other groups are still computing logits; the last group to finish builds the plan.
+#ifdef ZMOE_GEMM_STATS
+    rt[1] = now();
+#endif
     __threadfence();
     __syncthreads();
     if (tid == 0) s_ticket = atomicAdd(&a.ticket[1 + tg], 1u);
     __syncthreads();
     if (s_ticket != (unsigned)a.E - 1) return;
     __threadfence();
+#ifdef ZMOE_GEMM_STATS
+    rt[2] = now();
+#endif
 
     float *prob_s = reinterpret_cast<float *>(dyn) + (size_t)warp * 2 * a.E;
     float *sel_s = prob_s + a.E;
@@ -97,6 +108,9 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const Rou
     for (int t = t0 + warp; t < a.T && t < t0 + ROUTER_TPB; t += NW)
         route_token_warp(sp, a.logits + (size_t)t * a.E, a.logits + (size_t)t * a.E, a.bias,
                          a.ids + (size_t)t * a.K, a.weights + (size_t)t * a.K, prob_s, sel_s, lane);
+#ifdef ZMOE_GEMM_STATS
+    rt[3] = now();
+#endif
     __threadfence();
     __syncthreads();
     const unsigned n_tg = (unsigned)((a.T + ROUTER_TPB - 1) / ROUTER_TPB);
@@ -107,10 +121,22 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_decode_kernel(const Rou
     __syncthreads();
     if (s_ticket != n_tg - 1) return;
     __threadfence();
+#ifdef ZMOE_GEMM_STATS
+    rt[4] = now();
+#endif
     PlanOut po{a.plan.hdr, a.plan.active, a.plan.offs, a.plan.slot, a.plan.item_offs_gu, a.plan.item_offs_dn,
                a.plan.freq, a.plan.aoffs, a.plan.antok, a.nrt_gu, a.nrt_dn, a.plan.pos, a.plan.mt_gu, a.plan.mt_dn};
     build_plan_cta(a.ids, a.T * a.K, a.E, po, cnt_s, pre_s, ids_s);
     if (tid == 0) a.ticket[0] = 0u;
+#ifdef ZMOE_GEMM_STATS
+    // phases of the CTA that ends the kernel, in ns: logits + quantise, ticket, routing, ticket, plan; calls
+    __syncthreads();
+    rt[5] = now();
+    if (tid == 0 && a.stats) {
+        for (int i = 0; i < 5; ++i) atomicAdd(&a.stats[8 + i], rt[i + 1] - rt[i]);
+        atomicAdd(&a.stats[13], 1ull);
+    }
+#endif
 }
 
 int launch_router_decode(const RouterArgs &a, cudaStream_t st) {

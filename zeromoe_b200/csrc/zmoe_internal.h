@@ -62,6 +62,7 @@ struct RouterArgs {
     bool want_q8x = true;  // large batches: also quantise x into q8x (the tensor-core path does not read it)
     float *logits_part = nullptr;  // large batches: [ROUTER_MAX_SPLIT][T, E] partial logits of a k-split router GEMM, or null
     int n_sm = 0;
+    unsigned long long *stats = nullptr;   // phase timers of the decode router (builds with ZMOE_GEMM_STATS), or null
 };
 constexpr int ROUTER_MAX_SPLIT = 4;
 
