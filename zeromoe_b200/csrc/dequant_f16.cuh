@@ -21,12 +21,16 @@ __device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t *p) {  // 2-byte al
 
 // tables the converters read from shared memory
 struct DequantTables {
-    uint32_t grid;   // shared address of the IQ2_XXS selector table: 256 x 8 bytes
+    uint32_t grid;   // shared address of the IQ2_XXS selector table: 256 entries x IQ2_TABLE_COPIES copies x 8 bytes
 };
 
 // Entry e of the table: four 16-bit byte-permute selectors, one per pair of elements (2p, 2p+1).  With
 // i0, i1 the codes (0, 1, 2 for the magnitudes 8, 25, 43: their high nibbles) of the two elements, the
 // selector's nibbles are (2 i0, 2 i0 + 1, 2 i1, 2 i1 + 1): the two bytes of each fp16 table entry.
+// The table is kept in IQ2_TABLE_COPIES copies, entry e of copy c at index e * COPIES + c: lane l reads copy l % 16,
+// so the sixteen lanes of a half-warp's 8-byte loads always fall into sixteen different bank pairs whatever
+// entries the data asks for (one copy gave about three wavefronts per load from the data-dependent indices).
+constexpr int IQ2_TABLE_COPIES = 16;
 __device__ __forceinline__ void dequant_fill_tables(uint2 *grid_s) {
     for (int i = threadIdx.x; i < 256; i += blockDim.x) {
         const uint64_t g = k_iq2xxs_grid[i];
@@ -35,7 +39,8 @@ __device__ __forceinline__ void dequant_fill_tables(uint2 *grid_s) {
             const uint32_t i0 = (uint32_t)(g >> (16 * pp + 4)) & 3u, i1 = (uint32_t)(g >> (16 * pp + 12)) & 3u;
             w[pp] = 0x1010u + 0x22u * (i0 + 256u * i1);
         }
-        grid_s[i] = make_uint2(w[0] | (w[1] << 16), w[2] | (w[3] << 16));
+        const uint2 v = make_uint2(w[0] | (w[1] << 16), w[2] | (w[3] << 16));
+        for (int c = 0; c < IQ2_TABLE_COPIES; ++c) grid_s[i * IQ2_TABLE_COPIES + c] = v;
     }
 }
 
@@ -149,7 +154,7 @@ __device__ __forceinline__ void convert_raw<IQ2_XXS>(const RawW<IQ2_XXS> &r, int
     const uint32_t t1 = h2_bits(__floats2half2_rn(db * 43.f, 0.f));        // entry 2
 #pragma unroll
     for (int l = 0; l < 4; ++l) {
-        const uint2 sel = lds64(tb.grid + 8 * ((r.aux0 >> (8 * l)) & 255u));
+        const uint2 sel = lds64(tb.grid + 8 * (IQ2_TABLE_COPIES * ((r.aux0 >> (8 * l)) & 255u) + (threadIdx.x & (IQ2_TABLE_COPIES - 1))));
         // Sign bits of the eight elements: the seven stored ones and their parity (even number of minus
         // signs per group of eight).  Bit 2p goes to bit 15 and bit 2p+1 to bit 31 of word p with one
         // multiplication: s * (0x40008000 >> 2p) puts bit k of s at k + 15 - 2p and at k + 30 - 2p, the two

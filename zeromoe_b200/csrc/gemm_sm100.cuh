@@ -121,7 +121,7 @@ gemm_sm100_kernel(const GemmParams p, const __grid_constant__ GemmMaps maps) {
         raw_empty[GEMM_NRAW], acc_full, acc_empty;
     __shared__ uint32_t tmem_slot;
     __shared__ int s_tile_offs[GEMM_MAX_ACTIVE + 1];
-    __shared__ __align__(16) uint2 grid_s[TYPE == IQ2_XXS ? 256 : 2];
+    __shared__ __align__(16) uint2 grid_s[TYPE == IQ2_XXS ? 256 * IQ2_TABLE_COPIES : 2];
 
     // 1024-byte alignment of the operand tiles (required by the 128-byte swizzle)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
