@@ -223,7 +223,8 @@ __device__ __forceinline__ void q2k_block_dot(const uint32_t (&blk)[NM], uint32_
         for (int w = 0; w < 4; ++w) sc[m][w] = lds32(blk[m] + 4 * w);
         isum[m] = 0;
     }
-#pragma unroll
+    // the halves run as a loop (not unrolled: the consumer loop has to stay inside the instruction cache)
+#pragma unroll 1
     for (int n = 0; n < 2; ++n) {
         // the two units of this half: aq[h][4 * j + i] multiplies word i of the 16 bytes h, plane j
         uint32_t aq[2][16];
@@ -252,7 +253,7 @@ __device__ __forceinline__ void q2k_block_dot(const uint32_t (&blk)[NM], uint32_
                     S[j][h] = t >> (2 * j);
                 }
             }
-            const uint32_t s0 = sc[m][2 * n] & 0x0F0F0F0Fu, s1 = sc[m][2 * n + 1] & 0x0F0F0F0Fu;
+            const uint32_t s0 = (n ? sc[m][2] : sc[m][0]) & 0x0F0F0F0Fu, s1 = (n ? sc[m][3] : sc[m][1]) & 0x0F0F0F0Fu;
             int t = isum[m];
             t = dp2a_lo_su(pack16(S[0][0], S[0][1]), s0, t);
             t = dp2a_hi_su(pack16(S[1][0], S[1][1]), s0, t);
