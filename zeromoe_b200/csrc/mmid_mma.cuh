@@ -102,8 +102,10 @@ __device__ __forceinline__ void load_b_half(uint32_t qrow_blk, uint32_t (&bq)[4]
 // The 4-bit scale is multiplied into the quants (3 * 15 fits a byte), so one k32 instruction spans two
 // groups and a whole super-block accumulates in one s32.
 // rowA / rowB: the block in rows g and g+8.  FIRST: cm starts from zero.
+// Two accumulators (even and odd s) halve the chain of dependent instructions; the caller adds them.
 template <int N, bool FIRST>
-__device__ __forceinline__ void q2k_half(uint32_t rowA, uint32_t rowB, int c, const uint32_t (&bq)[4][2], int (&cm)[4]) {
+__device__ __forceinline__ void q2k_half(uint32_t rowA, uint32_t rowB, int c, const uint32_t (&bq)[4][2], int (&cm)[4],
+                                         int (&cx)[4]) {
     const uint32_t qA = rowA + 4 * c, qB = rowB + 4 * c;
     const uint32_t qa[2] = {ldso<16 + 32 * N>(qA), ldso<32 + 32 * N>(qA)};
     const uint32_t qb[2] = {ldso<16 + 32 * N>(qB), ldso<32 + 32 * N>(qB)};
@@ -117,8 +119,13 @@ __device__ __forceinline__ void q2k_half(uint32_t rowA, uint32_t rowB, int c, co
         const uint32_t a1 = ((qb[0] >> (2 * s)) & 0x03030303u) * __byte_perm(sB[w], 0, e0);
         const uint32_t a2 = ((qa[1] >> (2 * s)) & 0x03030303u) * __byte_perm(sA[w], 0, e1);
         const uint32_t a3 = ((qb[1] >> (2 * s)) & 0x03030303u) * __byte_perm(sB[w], 0, e1);
-        if (FIRST && s == 0) mma_u8s8_k32<true>(cm, a0, a1, a2, a3, bq[s][0], bq[s][1]);
-        else mma_u8s8_k32<false>(cm, a0, a1, a2, a3, bq[s][0], bq[s][1]);
+        if (s & 1) {
+            if (FIRST && s == 1) mma_u8s8_k32<true>(cx, a0, a1, a2, a3, bq[s][0], bq[s][1]);
+            else mma_u8s8_k32<false>(cx, a0, a1, a2, a3, bq[s][0], bq[s][1]);
+        } else {
+            if (FIRST && s == 0) mma_u8s8_k32<true>(cm, a0, a1, a2, a3, bq[s][0], bq[s][1]);
+            else mma_u8s8_k32<false>(cm, a0, a1, a2, a3, bq[s][0], bq[s][1]);
+        }
     }
 }
 // sum over the block's groups of min * (group sum of the activations), for the block in rows g and g+8
@@ -301,14 +308,19 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
             const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow1 + 4 * b));
             const uint32_t qblk = qrow + (uint32_t)(4 * b) * Q8_UNIT_STRIDE + 4 * c;
             const uint32_t boff = (uint32_t)b * BB;
-            int cm0[4], cm1[4];
+            int cm0[4], cm1[4], cx0[4], cx1[4];
             uint32_t bq[4][2];
             load_b_half<0>(qblk, bq);
-            q2k_half<0, true>(tile0 + offA + boff, tile0 + offB + boff, c, bq, cm0);
-            if (DUAL) q2k_half<0, true>(tile1 + offA + boff, tile1 + offB + boff, c, bq, cm1);
+            q2k_half<0, true>(tile0 + offA + boff, tile0 + offB + boff, c, bq, cm0, cx0);
+            if (DUAL) q2k_half<0, true>(tile1 + offA + boff, tile1 + offB + boff, c, bq, cm1, cx1);
             load_b_half<1>(qblk, bq);
-            q2k_half<1, false>(tile0 + offA + boff, tile0 + offB + boff, c, bq, cm0);
-            if (DUAL) q2k_half<1, false>(tile1 + offA + boff, tile1 + offB + boff, c, bq, cm1);
+            q2k_half<1, false>(tile0 + offA + boff, tile0 + offB + boff, c, bq, cm0, cx0);
+            if (DUAL) q2k_half<1, false>(tile1 + offA + boff, tile1 + offB + boff, c, bq, cm1, cx1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                cm0[i] += cx0[i];
+                if (DUAL) cm1[i] += cx1[i];
+            }
 #pragma unroll
             for (int m = 0; m < (DUAL ? 2 : 1); ++m) {
                 const uint32_t rowA = (m ? tile1 : tile0) + offA + boff, rowB = (m ? tile1 : tile0) + offB + boff;
