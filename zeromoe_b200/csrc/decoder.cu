@@ -61,6 +61,49 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(float *__restrict__ y, con
     }
 }
 
+// RMSNorm followed by the Q8_0 quantiser in one launch (the normed row only feeds a Q8_0 matmul): one CTA per
+// row, a thread owns four consecutive elements, the eight threads of a 32-element block share its maximum.
+// Same arithmetic, in the same order, as rmsnorm_kernel followed by quantize_q8_0_kernel.
+__global__ void __launch_bounds__(256) rmsnorm_q8_0_kernel(int8_t *__restrict__ q, float *__restrict__ d,
+                                                           const float *__restrict__ x, const float *__restrict__ w, int D,
+                                                           float eps) {
+    __shared__ float s_part[8];
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float4 *xv = reinterpret_cast<const float4 *>(x + (size_t)row * D);
+    const float4 *wv = reinterpret_cast<const float4 *>(w);
+    float ss = 0.f;
+    for (int i = tid; i < D / 4; i += 256) {
+        const float4 v = xv[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) s_part[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += s_part[i];
+    const float inv = rsqrtf(tot / (float)D + eps);
+    const int nb = D / 32;
+    // D is a multiple of 32: whole groups of eight threads run each iteration together
+    for (int i = tid; i < D / 4; i += 256) {
+        const float4 v = xv[i], g = wv[i];
+        const float y0 = v.x * inv * g.x, y1 = v.y * inv * g.y, y2 = v.z * inv * g.z, y3 = v.w * inv * g.w;
+        float amax = fmaxf(fmaxf(fabsf(y0), fabsf(y1)), fmaxf(fabsf(y2), fabsf(y3)));
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float dd = __fdiv_rn(amax, 127.f);
+        const float id = dd != 0.f ? __fdiv_rn(1.0f, dd) : 0.f;
+        char4 o4;
+        o4.x = (signed char)roundf(__fmul_rn(y0, id)); o4.y = (signed char)roundf(__fmul_rn(y1, id));
+        o4.z = (signed char)roundf(__fmul_rn(y2, id)); o4.w = (signed char)roundf(__fmul_rn(y3, id));
+        reinterpret_cast<char4 *>(q + (size_t)row * D)[i] = o4;
+        if ((tid & 7) == 0) d[(size_t)row * nb + (i >> 3)] = __half2float(__float2half_rn(dd));
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Q8_0 activation quantiser: one warp per block of 32 values.  q int8 [rows, I], d f32 [rows, I / 32] holds
 // the fp16-rounded scale (what the dot multiplies with).
@@ -547,8 +590,9 @@ int zmoe_decoder_step(zmoe_decoder *dec, const int32_t *tokens_dev, int T, void 
     count_launches(1);
     for (int l = 0; l < d.n_layers && !rc; ++l) {
         // ---- attention block: h += Wo . attention(rope(Wqkv . rmsnorm(h))) ----
-        rc = launch_rmsnorm_rows(dec->xn, dec->h, dec->attn_norm[l], T, D, d.rms_eps, st);
-        if (!rc) rc = launch_quantize_q8_0(dec->xn, D, dec->aq, dec->ad, T, D, st);
+        rc = cu(launch_pdl(rmsnorm_q8_0_kernel, dim3(T), dim3(256), 0, st, dec->aq, dec->ad, (const float *)dec->h,
+                           (const float *)dec->attn_norm[l], D, d.rms_eps));
+        count_launches(1);
         if (!rc) rc = launch_q8_0_mm(dec->qkv, dec->qkv_cols, dec->wqkv[l], dec->aq, dec->ad, T, D, dec->qkv_cols, 0, st);
         if (!rc) rc = cu(launch_pdl(rope_kv_kernel, dim3(T, H + KV), dim3(hd / 2), 0, st, dec->qkv, dec->kc + l * kv_layer,
                                     dec->vc + l * kv_layer, (const int *)dec->pos, H, KV, hd, theta_scale, d.max_ctx));
@@ -577,8 +621,11 @@ int zmoe_decoder_step(zmoe_decoder *dec, const int32_t *tokens_dev, int T, void 
         if (!rc) rc = zmoe_expert_ffn(dec->moe[l], dec->h, T, 1, stream);
     }
     // ---- output head on the last token, greedy sampling ----
-    if (!rc) rc = launch_rmsnorm_rows(dec->xn, dec->h + (size_t)(T - 1) * D, d.out_norm_w, 1, D, d.rms_eps, st);
-    if (!rc) rc = launch_quantize_q8_0(dec->xn, D, dec->aq, dec->ad, 1, D, st);
+    if (!rc) {
+        rc = cu(launch_pdl(rmsnorm_q8_0_kernel, dim3(1), dim3(256), 0, st, dec->aq, dec->ad,
+                           (const float *)(dec->h + (size_t)(T - 1) * D), (const float *)d.out_norm_w, D, d.rms_eps));
+        count_launches(1);
+    }
     if (!rc) rc = launch_q8_0_mm(dec->logits, d.vocab, d.lm_head, dec->aq, dec->ad, 1, D, d.vocab, 0, st);
     if (!rc) rc = cu(launch_pdl(argmax_kernel, dim3(1), dim3(1024), 0, st, (const float *)dec->logits, d.vocab, dec->next));
     if (!rc) rc = cu(launch_pdl(advance_pos_kernel, dim3(1), dim3(32), 0, st, dec->pos, T));
