@@ -55,6 +55,7 @@ static bool mmid2_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
         if ((size_t)stage * M2_NSET * M2_NSTG > (size_t)budget) continue;
         g->v2 = 1; g->maxtok = maxtok; g->cb = cb; g->acb = acb; g->nch = nb / cb; g->pitch = pitch; g->tiled = tiled ? 1 : 0;
         g->lb_log2 = cb * 4 > 16 ? 3 : 2;   // up to four units per lane
+        if (type == Q3_K) g->lb_log2 = 2;   // its one-pair path works on half super-blocks, four lanes to a row
         g->q8s_l = q8s_l;
         g->R = M2_R; g->wtile_bytes = wtile; g->stage_bytes = stage; g->nstage = M2_NSTG;
         g->smem_bytes = (size_t)stage * M2_NSET * M2_NSTG;

@@ -347,6 +347,29 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
                         }
                     }
                 }
+            } else if (TYPE == Q3_K && SC == 1) {
+                // four lanes per row (the geometry gives Q3_K lb_log2 == 2, so np == 1: a warp's lanes cover eight rows),
+                // each takes a run of half super-blocks
+                const int n_half = 2 * p.cb, hpl = (n_half + 3) >> 2;
+                if (m_ntok > 0) {
+#pragma unroll 1
+                    for (int i = 0; i < hpl; ++i) {
+                        const int hb = bl * hpl + i;
+                        if (hb >= n_half) break;
+                        const uint32_t roff = (uint32_t)(ws * rpp + rl) * p.pitch + (uint32_t)(hb >> 1) * BB;
+                        if (DUAL) {
+                            const uint32_t blk[2] = {t0 + roff, t1 + roff};
+                            float a[2] = {acc[0][0][0], acc[0][1][0]};
+                            q3k_half_dot<2>(blk, hb & 1, q8base, p.I_l, ab + (hb >> 1), a);
+                            acc[0][0][0] = a[0]; acc[0][1][0] = a[1];
+                        } else {
+                            const uint32_t blk[1] = {t0 + roff};
+                            float a[1] = {acc[0][0][0]};
+                            q3k_half_dot<1>(blk, hb & 1, q8base, p.I_l, ab + (hb >> 1), a);
+                            acc[0][0][0] = a[0];
+                        }
+                    }
+                }
             } else {
 #pragma unroll
                 for (int tk = 0; tk < SC; ++tk) {

@@ -179,9 +179,9 @@ __device__ __forceinline__ void unit_dot(uint32_t blk, int sub, const UnitAct &a
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
             slo = dp4a_us(qs[m] & 0x0F0F0F0Fu, a.q[m], slo);
-            shi = dp4a_us((qs[m] >> 4) & 0x0F0F0F0Fu, a.q[8 + m], shi);
+            shi = dp4a_us(qs[m] & 0xF0F0F0F0u, a.q[8 + m], shi);   // the high nibbles in place: 16 x the sum, exactly
         }
-        isum = sc_lo * slo + sc_hi * shi;
+        isum = sc_lo * slo + sc_hi * (shi >> 4);
         msum = m_lo * a.bs[0] + m_hi * a.bs[1];
     } else {  // IQ2_XXS: d @0, qs[32] u16 @2 ; unit = sub-blocks 2*sub, 2*sub+1
         uint32_t aux[4];
@@ -280,6 +280,73 @@ __device__ __forceinline__ void q2k_block_dot(const uint32_t (&blk)[NM], uint32_
         const float d = half_bits_to_float(dd), dmin = half_bits_to_float(dd >> 16);
         acc[m] = fmaf(d * d8, (float)isum[m], acc[m]);
         acc[m] = fmaf(-(dmin * d8), (float)ms, acc[m]);
+    }
+}
+
+// One half (128 elements: the units (n, h = 0, 1), scale groups 8n .. 8n + 7) of a Q3_K super-block of one row (of
+// two rows, NM = 2) against the matching half of an activation block.  Same integers as two unit_dot calls.  Done
+// once per half instead of once per unit: the eight six-bit scales (taken as signed bytes sc - 32, so that a dp2a
+// pairs the sums of the units h = 0, 1 with two adjacent scale bytes), the -4 offset of the quants (the same dp2a on
+// the group sums of the packed row, which sit in group order), d, and the int -> float conversion.  The 2-bit
+// planes and the high-bit plane stay in place under the dp4a: byte values q << 2j and 1 << (4n + j) give exact
+// multiples, which one shift per plane brings back.
+//   blk[m]: the block in shared memory (2-byte aligned); arow: the packed activation row; b: its block index
+//   acc[m] += d * d8 * isum
+template <int NM>
+__device__ __forceinline__ void q3k_half_dot(const uint32_t (&blk)[NM], int n, uint32_t arow, int I, int b, float (&acc)[NM]) {
+    uint32_t aq[2][16];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t base = arow + Q8_UNIT_STRIDE * (4 * b + 2 * n + h);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 v = lds128(base + 16 * j);
+            aq[h][4 * j + 0] = v.x; aq[h][4 * j + 1] = v.y; aq[h][4 * j + 2] = v.z; aq[h][4 * j + 3] = v.w;
+        }
+    }
+    const uint4 bw = lds128(arow + q8row_bs_off(I) + 32 * b + 16 * n);   // group sums 8n .. 8n + 7
+    const float d8 = __uint_as_float(lds32(arow + q8row_d_off(I) + 4 * b));
+    const uint32_t hbit = 0x01010101u << (4 * n);
+#pragma unroll
+    for (int m = 0; m < NM; ++m) {
+        // hmask[32] @0, qs[64] @32, scales[12] @96, d @108
+        uint32_t qs[8], hm[8], sc[3];
+        lds32xN_any<2, 8>(blk[m] + 32 + 32 * n, qs);
+        lds32xN_any<2, 8>(blk[m], hm);
+        lds32xN_any<2, 3>(blk[m] + 96, sc);
+        const float d = half_bits_to_float(lds16(blk[m] + 108));
+        int S[4][2];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                int tq = 0, th = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    tq = dp4a_us(qs[4 * h + i] & (0x03030303u << (2 * j)), (int)aq[h][4 * j + i], tq);
+                    th = dp4a_us(hm[4 * h + i] & (hbit << j), (int)aq[h][4 * j + i], th);
+                }
+                S[j][h] = (tq >> (2 * j)) + 4 * (th >> (4 * n + j));   // |S| <= 16*7*127: fits 16 bits
+            }
+        }
+        // scale of group 8n + i: low nibble = nibble n of byte i of the first eight bytes, high two bits = bits
+        // 4n + 2 * (i >> 2) of byte i & 3 of the last four
+        const uint32_t hs = sc[2] >> (4 * n);
+        uint32_t s0 = ((sc[0] >> (4 * n)) & 0x0F0F0F0Fu) | ((hs & 0x03030303u) << 4);
+        uint32_t s1 = ((sc[1] >> (4 * n)) & 0x0F0F0F0Fu) | (((hs >> 2) & 0x03030303u) << 4);
+        // bytes 0..63 -> signed bytes sc - 32 (the top bit keeps the bytes apart during the subtraction)
+        s0 = ((s0 | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
+        s1 = ((s1 | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
+        int t = dp2a_lo_ss(pack16(S[0][0], S[0][1]), s0, 0);
+        t = dp2a_hi_ss(pack16(S[1][0], S[1][1]), s0, t);
+        t = dp2a_lo_ss(pack16(S[2][0], S[2][1]), s1, t);
+        t = dp2a_hi_ss(pack16(S[3][0], S[3][1]), s1, t);
+        // q3 = (q2 | hbit << 2) - 4: minus 4 * scale * group sum
+        int u = dp2a_lo_ss(bw.x, s0, 0);
+        u = dp2a_hi_ss(bw.y, s0, u);
+        u = dp2a_lo_ss(bw.z, s1, u);
+        u = dp2a_hi_ss(bw.w, s1, u);
+        acc[m] = fmaf(d * d8, (float)(t - 4 * u), acc[m]);
     }
 }
 

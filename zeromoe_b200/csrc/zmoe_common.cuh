@@ -197,6 +197,17 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
     return d;
 }
 
+// dp2a with signed bytes in b
+__device__ __forceinline__ int dp2a_lo_ss(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.lo.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp2a_hi_ss(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp2a.hi.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 // dp2a: two signed 16-bit halves of a times two unsigned bytes of b (lo: bytes 0,1; hi: bytes 2,3)
 __device__ __forceinline__ int dp2a_lo_su(uint32_t a, uint32_t b, int c) {
     int d;
