@@ -102,7 +102,8 @@ __device__ __forceinline__ void load_b_half(uint32_t qrow_blk, uint32_t (&bq)[4]
 // The 4-bit scale is multiplied into the quants (3 * 15 fits a byte), so one k32 instruction spans two
 // groups and a whole super-block accumulates in one s32.
 // rowA / rowB: the block in rows g and g+8.  FIRST: cm starts from zero.
-// Two accumulators (even and odd s) halve the chain of dependent instructions; the caller adds them.
+// Two accumulators (even and odd s) halve the chain of dependent instructions; cx holds FOUR times the sums of the
+// odd planes (they are multiplied where they sit), the caller adds cm + (cx >> 2).
 template <int N, bool FIRST>
 __device__ __forceinline__ void q2k_half(uint32_t rowA, uint32_t rowB, int c, const uint32_t (&bq)[4][2], int (&cm)[4],
                                          int (&cx)[4]) {
@@ -115,10 +116,13 @@ __device__ __forceinline__ void q2k_half(uint32_t rowA, uint32_t rowB, int c, co
     for (int s = 0; s < 4; ++s) {
         const int w = s >> 1, by = (s & 1) * 2;   // groups 2s, 2s+1 of the half: bytes by, by+1 of word w
         const uint32_t e0 = 0x4440u | by, e1 = 0x4440u | (by + 1);
-        const uint32_t a0 = ((qa[0] >> (2 * s)) & 0x03030303u) * __byte_perm(sA[w], 0, e0);
-        const uint32_t a1 = ((qb[0] >> (2 * s)) & 0x03030303u) * __byte_perm(sB[w], 0, e0);
-        const uint32_t a2 = ((qa[1] >> (2 * s)) & 0x03030303u) * __byte_perm(sA[w], 0, e1);
-        const uint32_t a3 = ((qb[1] >> (2 * s)) & 0x03030303u) * __byte_perm(sB[w], 0, e1);
+        // odd s: the plane stays two bits up (bytes 4 * q * scale <= 180), so cx holds four times its sums
+        const int sh = 4 * (s >> 1);
+        const uint32_t mask = (s & 1) ? 0x0C0C0C0Cu : 0x03030303u;
+        const uint32_t a0 = ((qa[0] >> sh) & mask) * __byte_perm(sA[w], 0, e0);
+        const uint32_t a1 = ((qb[0] >> sh) & mask) * __byte_perm(sB[w], 0, e0);
+        const uint32_t a2 = ((qa[1] >> sh) & mask) * __byte_perm(sA[w], 0, e1);
+        const uint32_t a3 = ((qb[1] >> sh) & mask) * __byte_perm(sB[w], 0, e1);
         if (s & 1) {
             if (FIRST && s == 1) mma_u8s8_k32<true>(cx, a0, a1, a2, a3, bq[s][0], bq[s][1]);
             else mma_u8s8_k32<false>(cx, a0, a1, a2, a3, bq[s][0], bq[s][1]);
@@ -318,8 +322,8 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
             if (DUAL) q2k_half<1, false>(tile1 + offA + boff, tile1 + offB + boff, c, bq, cm1, cx1);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                cm0[i] += cx0[i];
-                if (DUAL) cm1[i] += cx1[i];
+                cm0[i] += cx0[i] >> 2;
+                if (DUAL) cm1[i] += cx1[i] >> 2;
             }
 #pragma unroll
             for (int m = 0; m < (DUAL ? 2 : 1); ++m) {
