@@ -163,19 +163,20 @@ __device__ __forceinline__ void q3k_half(uint32_t rowA, uint32_t rowB, int c, in
     const uint32_t hb[2] = {ldso_mis<MIS, 0>(qB) >> (4 * N), ldso_mis<MIS, 16>(qB) >> (4 * N)};
     // 6-bit scales of groups 8n + j: low nibbles in bytes 0..7 (low half for groups < 8), the two high
     // bits in bytes 8..11 at bit 2*(group / 4) of byte group % 4.  Bytes become sc6 - 32 (signed).
+    // The four lanes c of a row pair share the work: lane c unpacks word c & 1 of row A (c < 2) or row B, a shuffle
+    // inside the group of four hands the words round.
     uint32_t sA[2], sB[2];
     {
-        const uint32_t w0 = ldso_mis<MIS, 96>(rowA), w1 = ldso_mis<MIS, 100>(rowA), w2 = ldso_mis<MIS, 104>(rowA);
-        const uint32_t v0 = ldso_mis<MIS, 96>(rowB), v1 = ldso_mis<MIS, 100>(rowB), v2 = ldso_mis<MIS, 104>(rowB);
-        const uint32_t a0 = ((w0 >> (4 * N)) & 0x0F0F0F0Fu) | (((w2 >> (4 * N)) & 0x03030303u) << 4);
-        const uint32_t a1 = ((w1 >> (4 * N)) & 0x0F0F0F0Fu) | (((w2 >> (4 * N + 2)) & 0x03030303u) << 4);
-        const uint32_t b0 = ((v0 >> (4 * N)) & 0x0F0F0F0Fu) | (((v2 >> (4 * N)) & 0x03030303u) << 4);
-        const uint32_t b1 = ((v1 >> (4 * N)) & 0x0F0F0F0Fu) | (((v2 >> (4 * N + 2)) & 0x03030303u) << 4);
+        const uint32_t rowS = (c & 2) ? rowB : rowA;
+        const int ws = c & 1;
+        const uint32_t w = ldso_mis<MIS, 96>(rowS + 4 * ws), w2 = ldso_mis<MIS, 104>(rowS);
+        const uint32_t a = ((w >> (4 * N)) & 0x0F0F0F0Fu) | (((w2 >> (4 * N + 2 * ws)) & 0x03030303u) << 4);
         // bytes are < 64: with bit 7 set the subtraction cannot borrow across bytes
-        sA[0] = ((a0 | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
-        sA[1] = ((a1 | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
-        sB[0] = ((b0 | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
-        sB[1] = ((b1 | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
+        const uint32_t sx = ((a | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
+        sA[0] = __shfl_sync(0xffffffffu, sx, 0, 4);
+        sA[1] = __shfl_sync(0xffffffffu, sx, 1, 4);
+        sB[0] = __shfl_sync(0xffffffffu, sx, 2, 4);
+        sB[1] = __shfl_sync(0xffffffffu, sx, 3, 4);
     }
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
