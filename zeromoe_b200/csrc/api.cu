@@ -126,6 +126,7 @@ struct zmoe_ctx {
     PlanStore plan;
     int *err = nullptr;
     int *bad = nullptr;        // [2] NaN / Inf inputs seen by the fused SwiGLU epilogues
+    int *queue = nullptr;      // [4] item tickets of the decode matmuls (two per projection; every launch leaves them zero)
     unsigned *ticket = nullptr;
     float *x_stage = nullptr, *out_stage = nullptr;  // device staging of the host entry
     cudaStream_t host_stream = nullptr;
@@ -198,6 +199,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     rc |= c->plan.alloc(max_experts, (int)P);
     rc |= dev_alloc(&c->err, 1);
     rc |= dev_alloc(&c->bad, 2);
+    rc |= dev_alloc(&c->queue, 4);
     rc |= dev_alloc(&c->ticket, 1 + ROUTER_MAX_GROUPS);
     rc |= dev_alloc(&c->x_stage, (size_t)max_tokens * max_d_model);
     rc |= dev_alloc(&c->out_stage, (size_t)max_tokens * max_d_model);
@@ -206,6 +208,7 @@ int zmoe_ctx_create(int max_tokens, int max_d_model, int max_d_ff, int max_exper
     if (!rc) {
         rc |= ok(cudaMemset(c->err, 0, sizeof(int)));
         rc |= ok(cudaMemset(c->bad, 0, 2 * sizeof(int)));
+        rc |= ok(cudaMemset(c->queue, 0, 4 * sizeof(int)));
         rc |= ok(cudaMemset(c->ticket, 0, (1 + ROUTER_MAX_GROUPS) * sizeof(unsigned)));
         rc |= ok(cudaMemset(c->plan.b.hdr, 0, 4 * sizeof(int)));
         rc |= ok(cudaMemset(c->zero_ids, 0, (size_t)max_tokens * sizeof(int32_t)));
@@ -233,7 +236,7 @@ void zmoe_ctx_destroy(zmoe_ctx *c) {
     cudaFree(c->zero_ids); cudaFree(c->one_w); cudaFree(c->gate_s);
     cudaFree(c->xq_f16); cudaFree(c->actq_f16); cudaFree(c->xscale); cudaFree(c->actscale);
     cudaFree(c->q8x); cudaFree(c->q8x2); cudaFree(c->act); cudaFree(c->act2); cudaFree(c->q8act); cudaFree(c->ydown);
-    cudaFree(c->logits); cudaFree(c->logits_part); cudaFree(c->ids); cudaFree(c->weights); cudaFree(c->err); cudaFree(c->bad); cudaFree(c->ticket);
+    cudaFree(c->logits); cudaFree(c->logits_part); cudaFree(c->ids); cudaFree(c->weights); cudaFree(c->err); cudaFree(c->bad); cudaFree(c->queue); cudaFree(c->ticket);
     cudaFree(c->x_stage); cudaFree(c->out_stage);
     c->plan.release();
     if (c->host_stream) cudaStreamDestroy(c->host_stream);
@@ -460,6 +463,7 @@ int zmoe_expert_ffn_events(zmoe_layer *L, float *out_dev, int T, int accumulate,
     m.plan = c->plan.b;
     m.err = c->err;
     m.bad = c->bad;
+    m.queue = c->queue;
     m.n_sm = c->n_sm;
     m.clamp = d.swiglu_clamp;
     m.clamp_fused = d.swiglu_clamp_fused;
@@ -605,6 +609,7 @@ int zmoe_moe_forward_host(zmoe_layer *L, const float *x_host, float *out_host, i
     if (!rc) rc = ok(cudaStreamSynchronize(c->host_stream));
     if (!rc && *c->err_host) {
         cudaMemset(c->err, 0, sizeof(int));
+        cudaMemset(c->queue, 0, 4 * sizeof(int));   // a launch that gave up may have left its tickets behind
         rc = ZMOE_ERR_DEVICE_WAIT;
     }
     return rc;
@@ -654,6 +659,7 @@ int zmoe_ctx_check(zmoe_ctx *c) {
     if (cudaMemcpy(&e, c->err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return ZMOE_ERR_CUDA;
     if (e) {
         cudaMemset(c->err, 0, sizeof(int));
+        cudaMemset(c->queue, 0, 4 * sizeof(int));   // a launch that gave up may have left its tickets behind
         return ZMOE_ERR_DEVICE_WAIT;
     }
     return ZMOE_OK;

@@ -215,6 +215,7 @@ static int launch_mmid2(const MmidLaunch &L, const MmidGeom &g, cudaStream_t st)
     p.stage_bytes = g.stage_bytes; p.wtile_bytes = g.wtile_bytes;
     p.err = L.err;
     p.bad = L.dual ? L.bad : nullptr;
+    p.queue = L.queue ? L.queue + (L.down ? 2 : 0) : nullptr;
     p.stats = gemm_stats_buffer(L.down ? 1 : 0);
     return launch_pdl(fn, dim3(L.n_sm), dim3(32 * (M2_NCW + 4)), g.smem_bytes, st, p) == cudaSuccess ? ZMOE_OK : ZMOE_ERR_CUDA;
 }

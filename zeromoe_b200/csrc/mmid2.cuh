@@ -59,6 +59,7 @@ struct M2Params {
     int clamp_fused;
     int stage_bytes, wtile_bytes;
     int *err, *bad;
+    int *queue;      // [2] ticket counter and finished-producer counter, both zero between launches; or null
     unsigned long long *stats;   // cycle counters (builds with ZMOE_GEMM_STATS only), or null
     alignas(64) CUtensorMap tm0, tm1;
 };
@@ -150,11 +151,13 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
         // item descriptor: e, r0, nrows, ntok and, in lane t < ntok, pair t
         struct Item { int e, r0, nrows, ntok, pair; };
         auto take = [&](Item &it) -> bool {
+            // with a ticket counter the next item goes to whichever set of the grid is free first (items differ in
+            // cost by their path); without one, items are dealt round-robin over the grid and a CTA's sets share them
             int j = 0;
-            if (lane == 0) j = atomicAdd(&s_next, 1);
+            if (lane == 0) j = p.queue ? atomicAdd(p.queue, 1) : atomicAdd(&s_next, 1);
             j = __shfl_sync(0xffffffffu, j, 0);
-            if (j >= n_mine) return false;
-            const int mine = (int)blockIdx.x + j * G;   // items are dealt round-robin over the grid
+            if (j >= (p.queue ? n_items : n_mine)) return false;
+            const int mine = p.queue ? j : (int)blockIdx.x + j * G;
             // last a with item_offs[a] <= mine: the lanes probe 32 points of the range at once
             int lo = 0, hi = n_active - 1;
             while (lo < hi) {
@@ -257,6 +260,13 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
             } else if (lane == 0) {
                 meta[s][slot].flags = 2;
                 mbar_arrive(&full_bar[s][slot]);
+            }
+        }
+        // the last producer of the grid to finish leaves the counters zero for the next launch
+        if (p.queue && lane == 0) {
+            if (atomicAdd(p.queue + 1, 1) == M2_NSET * G - 1) {
+                p.queue[0] = 0;
+                p.queue[1] = 0;
             }
         }
         M2STAT_ADD(2, st_idle); M2STAT_ADD(3, st_busy); M2STAT_ADD(4, st_fills);

@@ -105,6 +105,8 @@ struct MmidLaunch {
     int clamp_fused;
     int *err;
     int *bad = nullptr;    // [2] NaN / Inf counters of the fused SwiGLU epilogue, or null
+    int *queue = nullptr;  // [4] zeroed ints: the chunked kernel deals its items through a ticket counter (two ints per
+                           // projection, left zero by every launch); null = items dealt round-robin over the grid
     int n_sm;
     bool multi = false;    // some expert may hold two or more pairs: allow the tensor-core consumer path
     // optional tiled maps of w0 / w1 (make_rows_map) that deliver tiles with padded rows in one copy
