@@ -75,7 +75,7 @@ struct M2Params {
 #define M2STAT_ADD(slot, v) do { } while (0)
 #endif
 
-struct M2Meta {
+struct alignas(16) M2Meta {
     int expert, r0, nrows, ntok;
     int chunk, flags;          // flags: 1 = last chunk of the item, 2 = no more items for this set
     int w0_off, w1_off;
@@ -147,9 +147,18 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
         const uint32_t act_bytes = p.nch == 1 ? (uint32_t)p.q8_stride
                                               : (uint32_t)(p.acb * 4 * Q8_UNIT_STRIDE + ((p.acb * 4 + 15) & ~15) + p.acb * 32);
         const int cpa = p.acb / p.cb;
+        // what a fill needs and what does not change from fill to fill, computed once: the producer shares its
+        // scheduler with three consumer warps and every instruction of a fill delays the stage
+        const uint32_t ub = (uint32_t)(p.acb * 4 * Q8_UNIT_STRIDE), db = (uint32_t)((p.acb * 4 + 15) & ~15), sb = (uint32_t)(p.acb * 32);
+        const uint32_t d_off_l = (uint32_t)q8row_d_off(p.I_l), bs_off_l = (uint32_t)q8row_bs_off(p.I_l);
+        const uint32_t d_off_g = (uint32_t)q8row_d_off(p.I), bs_off_g = (uint32_t)q8row_bs_off(p.I);
+        const uint32_t d_step = (uint32_t)(p.acb * 4);
+        const uint32_t wbytes = (uint32_t)(M2_R * p.pitch) * (DUAL ? 2u : 1u);
+        const uint32_t q8_lane = (uint32_t)((DUAL ? 2 : 1) * p.wtile_bytes) + (uint32_t)lane * (uint32_t)p.q8s_l;
+        const int xstep = p.cbytes >> 3;   // the maps count in 8-byte elements
         long long st_idle = 0, st_busy = 0, st_fills = 0;
         // item descriptor: e, r0, nrows, ntok and, in lane t < ntok, pair t
-        struct Item { int e, r0, nrows, ntok, pair; };
+        struct Item { int e, r0, nrows, ntok, pair; const uint8_t *src; };   // src: the pair's packed activation row
         auto take = [&](Item &it) -> bool {
             // with a ticket counter the next item goes to whichever set of the grid is free first (items differ in
             // cost by their path); without one, items are dealt round-robin over the grid and a CTA's sets share them
@@ -184,6 +193,7 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
             it.nrows = min(M2_R, p.O - it.r0);
             it.ntok = min(p.maxtok, ecnt - tc * p.maxtok);
             it.pair = lane < it.ntok ? p.plan.slot[ebase + tc * p.maxtok + lane] : 0;
+            it.src = p.q8 + (size_t)(it.pair / p.xdiv) * p.q8_stride;
             return true;
         };
         Item cur, nxt;
@@ -191,7 +201,10 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
         int f = 0;
         bool alive = true;
         while (have && alive) {
-            const bool have_next = take(nxt);   // its loads complete while this item's chunks go out
+            bool have_next = false;
+            // this item's activation slices, walked chunk by chunk
+            const uint8_t *su = cur.src, *sd = cur.src + d_off_g, *sbs = cur.src + bs_off_g;
+            int x = 0, cc = 0;
             for (int c = 0; c < p.nch; ++c, ++f) {
                 const int slot = f % M2_NSTG;
                 const long long st_t0 = M2STAT_NOW();
@@ -203,51 +216,49 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
                 const long long st_t1 = M2STAT_NOW();
                 M2Meta &m = meta[s][slot];
                 uint8_t *stage = smem + (size_t)(s * M2_NSTG + slot) * p.stage_bytes;
-                uint8_t *q8dst = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
+                uint64_t *bar = &full_bar[s][slot];
                 uint32_t bytes = 0;
                 if (lane == 0) {
-                    m.expert = cur.e; m.r0 = cur.r0; m.nrows = cur.nrows; m.ntok = cur.ntok;
-                    m.chunk = c; m.flags = c + 1 == p.nch ? 1 : 0;
-                    m.w0_off = 0; m.w1_off = 0;
+                    int w0_off = 0, w1_off = 0;
                     if (p.tiled) {
                         // the box is always 32 full rows of `pitch` bytes: rows past the expert's last and bytes past
                         // the row's end arrive as zeros
-                        const int x = (c * p.cbytes) >> 3;   // the maps count in 8-byte elements
-                        tma_load_chunk(stage, &p.tm0, x, cur.r0, cur.e, &full_bar[s][slot]);
-                        if (DUAL) tma_load_chunk(stage + p.wtile_bytes, &p.tm1, x, cur.r0, cur.e, &full_bar[s][slot]);
-                        bytes = (uint32_t)(M2_R * p.pitch) * (DUAL ? 2u : 1u);
+                        tma_load_chunk(stage, &p.tm0, x, cur.r0, cur.e, bar);
+                        if (DUAL) tma_load_chunk(stage + p.wtile_bytes, &p.tm1, x, cur.r0, cur.e, bar);
+                        bytes = wbytes;
                     } else {
                         const size_t g0 = (size_t)cur.e * p.stride0 + (size_t)cur.r0 * p.rb;
-                        bytes += issue_tile(stage, p.w0, p.total0, g0, g0 + (size_t)cur.nrows * p.rb, &full_bar[s][slot], &m.w0_off);
+                        bytes += issue_tile(stage, p.w0, p.total0, g0, g0 + (size_t)cur.nrows * p.rb, bar, &w0_off);
                         if (DUAL) {
                             const size_t h0 = (size_t)cur.e * p.stride1 + (size_t)cur.r0 * p.rb;
-                            bytes += issue_tile(stage + p.wtile_bytes, p.w1, p.total1, h0, h0 + (size_t)cur.nrows * p.rb,
-                                                &full_bar[s][slot], &m.w1_off);
+                            bytes += issue_tile(stage + p.wtile_bytes, p.w1, p.total1, h0, h0 + (size_t)cur.nrows * p.rb, bar, &w1_off);
                         }
                     }
+                    *reinterpret_cast<int4 *>(&m.expert) = make_int4(cur.e, cur.r0, cur.nrows, cur.ntok);
+                    *reinterpret_cast<int4 *>(&m.chunk) = make_int4(c, c + 1 == p.nch ? 1 : 0, w0_off, w1_off);
                 }
                 if (lane < cur.ntok) {
                     // this chunk's slice of the pair's packed activation row, laid out as a row of I_l elements
                     m.pair[lane] = cur.pair;
-                    const uint8_t *src = p.q8 + (size_t)(cur.pair / p.xdiv) * p.q8_stride;
-                    uint8_t *dst = q8dst + (size_t)lane * p.q8s_l;
+                    uint8_t *dst = stage + q8_lane;
                     if (p.nch == 1) {
-                        bulk_g2s(dst, src, (uint32_t)p.q8_stride, &full_bar[s][slot]);
+                        bulk_g2s(dst, cur.src, (uint32_t)p.q8_stride, bar);
                     } else {
-                        const uint32_t ub = (uint32_t)(p.acb * 4 * Q8_UNIT_STRIDE), db = (uint32_t)((p.acb * 4 + 15) & ~15),
-                                       sb = (uint32_t)(p.acb * 32);
-                        const int ca = c / cpa;
-                        bulk_g2s(dst, src + (size_t)ca * ub, ub, &full_bar[s][slot]);
-                        bulk_g2s(dst + q8row_d_off(p.I_l), src + q8row_d_off(p.I) + ca * p.acb * 4, db, &full_bar[s][slot]);
-                        bulk_g2s(dst + q8row_bs_off(p.I_l), src + q8row_bs_off(p.I) + ca * p.acb * 32, sb, &full_bar[s][slot]);
+                        bulk_g2s(dst, su, ub, bar);
+                        bulk_g2s(dst + d_off_l, sd, db, bar);
+                        bulk_g2s(dst + bs_off_l, sbs, sb, bar);
                     }
                 }
                 __syncwarp();
                 // the producer's own arrival, with the byte count, is what lets the phase complete
-                if (lane == 0) mbar_arrive_expect_tx(&full_bar[s][slot], bytes + (uint32_t)cur.ntok * act_bytes);
+                if (lane == 0) mbar_arrive_expect_tx(bar, bytes + (uint32_t)cur.ntok * act_bytes);
+                x += xstep;
+                if (++cc == cpa) { cc = 0; su += ub; sd += d_step; sbs += sb; }
                 st_idle += st_t1 - st_t0;
                 st_busy += M2STAT_NOW() - st_t1;
                 ++st_fills;
+                // the next item is resolved once this item's first chunk is on its way
+                if (c == 0) have_next = take(nxt);
             }
             cur = nxt;
             have = have_next;
