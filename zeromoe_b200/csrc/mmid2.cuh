@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
             const uint32_t t1 = stage + p.wtile_bytes + m.w1_off;
             const uint32_t q8base = stage + (DUAL ? 2 : 1) * p.wtile_bytes;
             const bool mma_item = MMA && m_ntok >= 2;
-            const int ab = (m.chunk % cpa) * p.cb;   // where the chunk's blocks sit inside the activation slice
+            const int ab = (m.chunk & (cpa - 1)) * p.cb;   // where the chunk's blocks sit inside the activation slice (cpa is 1 or 2)
             if (m.chunk == 0) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) f0[i] = 0.f;

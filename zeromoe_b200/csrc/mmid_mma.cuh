@@ -164,7 +164,7 @@ __device__ __forceinline__ void q3k_half(uint32_t rowA, uint32_t rowB, int c, in
     // 6-bit scales of groups 8n + j: low nibbles in bytes 0..7 (low half for groups < 8), the two high
     // bits in bytes 8..11 at bit 2*(group / 4) of byte group % 4.  Bytes become sc6 - 32 (signed).
     // The four lanes c of a row pair share the work: lane c unpacks word c & 1 of row A (c < 2) or row B, a shuffle
-    // inside the group of four hands the words round.
+    // inside the group of four passes the words on.
     uint32_t sA[2], sB[2];
     {
         const uint32_t rowS = (c & 2) ? rowB : rowA;
