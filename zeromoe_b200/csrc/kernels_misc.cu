@@ -362,9 +362,9 @@ __global__ void q8rows_to_blocks_kernel(const uint8_t *q8, uint8_t *blocks, int 
     const int r = idx / nb, b = idx % nb;
     const uint8_t *row = q8 + (size_t)r * stride;
     uint8_t *o = blocks + (size_t)idx * 292;
-    for (int i = 0; i < 4; ++i) o[i] = row[q8row_d_off(I) + 4 * b + i];
+    for (int i = 0; i < 4; ++i) o[i] = row[q8_d_off(b) + i];
     for (int i = 0; i < 256; ++i) o[4 + i] = row[q8row_elem_off(layout, b, i)];
-    for (int i = 0; i < 32; ++i) o[260 + i] = row[q8row_bs_off(I) + 32 * b + i];
+    for (int i = 0; i < 32; ++i) o[260 + i] = row[q8_bs_off(b) + i];
 }
 
 int launch_q8rows_to_blocks(const uint8_t *q8, uint8_t *blocks, int rows, int I, int layout, cudaStream_t st) {

@@ -144,15 +144,12 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
         // while the previous item's chunks are still being issued, and feeds its set's two stages.
         const int s = warp - M2_NCW;
         if (s >= M2_NSET) return;
-        const uint32_t act_bytes = p.nch == 1 ? (uint32_t)p.q8_stride
-                                              : (uint32_t)(p.acb * 4 * Q8_UNIT_STRIDE + ((p.acb * 4 + 15) & ~15) + p.acb * 32);
+        // a pair's activations for one stage: the whole packed row, or the slice of acb blocks the chunk meets (the
+        // packed row is stored block by block, so a slice is one run of bytes)
+        const uint32_t act_bytes = p.nch == 1 ? (uint32_t)p.q8_stride : (uint32_t)(p.acb * Q8_BLOCK_STRIDE);
         const int cpa = p.acb / p.cb;
         // what a fill needs and what does not change from fill to fill, computed once: the producer shares its
         // scheduler with three consumer warps and every instruction of a fill delays the stage
-        const uint32_t ub = (uint32_t)(p.acb * 4 * Q8_UNIT_STRIDE), db = (uint32_t)((p.acb * 4 + 15) & ~15), sb = (uint32_t)(p.acb * 32);
-        const uint32_t d_off_l = (uint32_t)q8row_d_off(p.I_l), bs_off_l = (uint32_t)q8row_bs_off(p.I_l);
-        const uint32_t d_off_g = (uint32_t)q8row_d_off(p.I), bs_off_g = (uint32_t)q8row_bs_off(p.I);
-        const uint32_t d_step = (uint32_t)(p.acb * 4);
         const uint32_t wbytes = (uint32_t)(M2_R * p.pitch) * (DUAL ? 2u : 1u);
         const uint32_t q8_lane = (uint32_t)((DUAL ? 2 : 1) * p.wtile_bytes) + (uint32_t)lane * (uint32_t)p.q8s_l;
         const int xstep = p.cbytes >> 3;   // the maps count in 8-byte elements
@@ -203,7 +200,7 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
         while (have && alive) {
             bool have_next = false;
             // this item's activation slices, walked chunk by chunk
-            const uint8_t *su = cur.src, *sd = cur.src + d_off_g, *sbs = cur.src + bs_off_g;
+            const uint8_t *su = cur.src;
             int x = 0, cc = 0;
             for (int c = 0; c < p.nch; ++c, ++f) {
                 const int slot = f % M2_NSTG;
@@ -241,19 +238,13 @@ __global__ void __launch_bounds__(32 * (M2_NCW + 4), 1) mmid2_kernel(const __gri
                     // this chunk's slice of the pair's packed activation row, laid out as a row of I_l elements
                     m.pair[lane] = cur.pair;
                     uint8_t *dst = stage + q8_lane;
-                    if (p.nch == 1) {
-                        bulk_g2s(dst, cur.src, (uint32_t)p.q8_stride, bar);
-                    } else {
-                        bulk_g2s(dst, su, ub, bar);
-                        bulk_g2s(dst + d_off_l, sd, db, bar);
-                        bulk_g2s(dst + bs_off_l, sbs, sb, bar);
-                    }
+                    bulk_g2s(dst, su, act_bytes, bar);
                 }
                 __syncwarp();
                 // the producer's own arrival, with the byte count, is what lets the phase complete
                 if (lane == 0) mbar_arrive_expect_tx(bar, bytes + (uint32_t)cur.ntok * act_bytes);
                 x += xstep;
-                if (++cc == cpa) { cc = 0; su += ub; sd += d_step; sbs += sb; }
+                if (++cc == cpa) { cc = 0; su += act_bytes; }
                 st_idle += st_t1 - st_t0;
                 st_busy += M2STAT_NOW() - st_t1;
                 ++st_fills;

@@ -300,18 +300,18 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
     const int g = lane >> 2, c = lane & 3;
     const uint32_t offA = (uint32_t)g * rb, offB = (uint32_t)(g + 8) * rb;
     const uint32_t qrow = q8rows + (uint32_t)min(g & (NT - 1), maxrow) * q8_stride;   // column g's activations
-    const uint32_t drow = q8rows + (uint32_t)min((2 * c) & (NT - 1), maxrow) * q8_stride + (uint32_t)q8row_d_off(I);
-    const uint32_t drow1 = q8rows + (uint32_t)min(((2 * c) & (NT - 1)) + 1, maxrow) * q8_stride + (uint32_t)q8row_d_off(I);
-    const uint32_t bs_off = (uint32_t)q8row_bs_off(I) + 8 * c;
+    const uint32_t drow = q8rows + (uint32_t)min((2 * c) & (NT - 1), maxrow) * q8_stride + (uint32_t)Q8_BLOCK_D;
+    const uint32_t drow1 = q8rows + (uint32_t)min(((2 * c) & (NT - 1)) + 1, maxrow) * q8_stride + (uint32_t)Q8_BLOCK_D;
+    const uint32_t bs_off = (uint32_t)Q8_BLOCK_BS + 8 * c;
     if (TYPE == Q2_K) {
         for (int b = hb0 >> 1; b < (hb1 >> 1); ++b) {
             uint32_t bs_hi, bs_lo;
             {
-                const uint2 w = lds64(qrow + bs_off + 32 * b);
+                const uint2 w = lds64(qrow + bs_off + Q8_BLOCK_STRIDE * b);
                 bsum_planes(w.x, w.y, bs_hi, bs_lo);
             }
-            const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow1 + 4 * b));
-            const uint32_t qblk = qrow + (uint32_t)(4 * b) * Q8_UNIT_STRIDE + 4 * c;
+            const float dx0 = __uint_as_float(lds32(drow + Q8_BLOCK_STRIDE * b)), dx1 = __uint_as_float(lds32(drow1 + Q8_BLOCK_STRIDE * b));
+            const uint32_t qblk = qrow + (uint32_t)b * Q8_BLOCK_STRIDE + 4 * c;
             const uint32_t boff = (uint32_t)b * BB;
             int cm0[4], cm1[4], cx0[4], cx1[4];
             uint32_t bq[4][2];
@@ -347,9 +347,9 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
         for (int b = hb0 >> 1; b < (hb1 >> 1); ++b) {
             // group sums of sub-blocks 4c'..4c'+3, c' = c & 1; lanes with c >= 2 multiply them by zero mins
             uint32_t bs_hi, bs_lo;
-            bsum_pair_planes(lds128(qrow + (uint32_t)q8row_bs_off(I) + 32 * b + 16 * (c & 1)), bs_hi, bs_lo);
-            const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow1 + 4 * b));
-            const uint32_t qblk = qrow + (uint32_t)(4 * b) * Q8_UNIT_STRIDE + 4 * c;
+            bsum_pair_planes(lds128(qrow + (uint32_t)q8_bs_off(b) + 16 * (c & 1)), bs_hi, bs_lo);
+            const float dx0 = __uint_as_float(lds32(drow + Q8_BLOCK_STRIDE * b)), dx1 = __uint_as_float(lds32(drow1 + Q8_BLOCK_STRIDE * b));
+            const uint32_t qblk = qrow + (uint32_t)b * Q8_BLOCK_STRIDE + 4 * c;
             const uint32_t boff = (uint32_t)b * BB;
 #pragma unroll
             for (int m = 0; m < (DUAL ? 2 : 1); ++m) {
@@ -381,10 +381,10 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
             const int b = hb >> 1;
             uint32_t bs_hi, bs_lo;
             {
-                const uint2 w = lds64(qrow + bs_off + 32 * b);
+                const uint2 w = lds64(qrow + bs_off + Q8_BLOCK_STRIDE * b);
                 bsum_planes(w.x, w.y, bs_hi, bs_lo);
             }
-            const uint32_t qblk = qrow + (uint32_t)(4 * b) * Q8_UNIT_STRIDE + 4 * c;
+            const uint32_t qblk = qrow + (uint32_t)b * Q8_BLOCK_STRIDE + 4 * c;
             const uint32_t boff = (uint32_t)b * BB;
             uint32_t bq[4][2];
             // blocks of 110 bytes: every other block starts 2 modulo 4, the same for all lanes
@@ -401,7 +401,7 @@ __device__ __forceinline__ void mma_rows(uint32_t tile0, uint32_t tile1, int rb,
             }
             if ((hb & 1) == 1 || hb + 1 == hb1) {
                 // the super-block (or this warp's share of it) is complete: scale into f32
-                const float dx0 = __uint_as_float(lds32(drow + 4 * b)), dx1 = __uint_as_float(lds32(drow1 + 4 * b));
+                const float dx0 = __uint_as_float(lds32(drow + Q8_BLOCK_STRIDE * b)), dx1 = __uint_as_float(lds32(drow1 + Q8_BLOCK_STRIDE * b));
 #pragma unroll
                 for (int m = 0; m < (DUAL ? 2 : 1); ++m) {
                     const uint32_t t = m ? tile1 : tile0;

@@ -52,8 +52,8 @@ __device__ __forceinline__ void quantize_block_q8k(const float *__restrict__ src
     int s = q[0] + q[1] + q[2] + q[3] + q[4] + q[5] + q[6] + q[7];
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     if ((lane & 1) == 0)
-        *reinterpret_cast<int16_t *>(row_out + q8row_bs_off(I) + 32 * b + 2 * (lane >> 1)) = (int16_t)s;
-    if (lane == 0) *reinterpret_cast<float *>(row_out + q8row_d_off(I) + 4 * b) = d;
+        *reinterpret_cast<int16_t *>(row_out + q8_bs_off(b) + 2 * (lane >> 1)) = (int16_t)s;
+    if (lane == 0) *reinterpret_cast<float *>(row_out + q8_d_off(b)) = d;
 }
 
 }  // namespace zmoe

@@ -52,9 +52,9 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 template <int TYPE>
 __device__ __forceinline__ void load_unit_act(uint32_t row, int I, int u, UnitAct &a) {
     const int b = u >> 2, sub = u & 3;
-    a.d = __uint_as_float(lds32(row + q8row_d_off(I) + 4 * b));
-    const uint32_t bs = row + q8row_bs_off(I) + 32 * b;
-    const uint32_t base = row + Q8_UNIT_STRIDE * u;
+    a.d = __uint_as_float(lds32(row + q8_d_off(b)));
+    const uint32_t bs = row + q8_bs_off(b);
+    const uint32_t base = row + q8_unit_off(u);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const uint4 v = lds128(base + 16 * j);
@@ -230,7 +230,7 @@ __device__ __forceinline__ void q2k_block_dot(const uint32_t (&blk)[NM], uint32_
         uint32_t aq[2][16];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t base = arow + Q8_UNIT_STRIDE * (4 * b + 2 * n + h);
+            const uint32_t base = arow + Q8_BLOCK_STRIDE * b + Q8_UNIT_STRIDE * (2 * n + h);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint4 v = lds128(base + 16 * j);
@@ -263,10 +263,10 @@ __device__ __forceinline__ void q2k_block_dot(const uint32_t (&blk)[NM], uint32_
         }
     }
     // mins: word w of the group sums holds groups 2w, 2w + 1; byte g of the min nibbles is group g
-    const uint32_t bs = arow + q8row_bs_off(I) + 32 * b;
+    const uint32_t bs = arow + q8_bs_off(b);
     const uint4 b0 = lds128(bs), b1 = lds128(bs + 16);
     const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-    const float d8 = __uint_as_float(lds32(arow + q8row_d_off(I) + 4 * b));
+    const float d8 = __uint_as_float(lds32(arow + q8_d_off(b)));
 #pragma unroll
     for (int m = 0; m < NM; ++m) {
         int ms = 0;
@@ -297,15 +297,15 @@ __device__ __forceinline__ void q3k_half_dot(const uint32_t (&blk)[NM], int n, u
     uint32_t aq[2][16];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const uint32_t base = arow + Q8_UNIT_STRIDE * (4 * b + 2 * n + h);
+        const uint32_t base = arow + Q8_BLOCK_STRIDE * b + Q8_UNIT_STRIDE * (2 * n + h);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint4 v = lds128(base + 16 * j);
             aq[h][4 * j + 0] = v.x; aq[h][4 * j + 1] = v.y; aq[h][4 * j + 2] = v.z; aq[h][4 * j + 3] = v.w;
         }
     }
-    const uint4 bw = lds128(arow + q8row_bs_off(I) + 32 * b + 16 * n);   // group sums 8n .. 8n + 7
-    const float d8 = __uint_as_float(lds32(arow + q8row_d_off(I) + 4 * b));
+    const uint4 bw = lds128(arow + q8_bs_off(b) + 16 * n);   // group sums 8n .. 8n + 7
+    const float d8 = __uint_as_float(lds32(arow + q8_d_off(b)));
     const uint32_t hbit = 0x01010101u << (4 * n);
 #pragma unroll
     for (int m = 0; m < NM; ++m) {

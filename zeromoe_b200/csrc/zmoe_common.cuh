@@ -19,9 +19,11 @@ __host__ __device__ constexpr int block_bytes(int type) {
 }
 
 // ---------------------------------------------------------------------------
-// Packed activation rows.  One Q8_K-quantised row of I elements is stored as a
-// single contiguous record so that one bulk copy brings it to shared memory:
-//   [ units: (I/64) x 80 bytes | float d[nb] (padded to 16 B) | int16 bsums[16*nb] ]
+// Packed activation rows.  One Q8_K-quantised row of I elements is stored block by
+// block, every super-block a record of 368 bytes:
+//   [ 4 units x 80 bytes | float d (padded to 16 B) | int16 bsums[16] ]
+// so that one bulk copy brings a row -- or the slice of a row that a chunk of weight
+// blocks meets -- to shared memory.
 // Same numbers as the 292-byte ggml block (reference backends/cpu/kernels_cpu.cpp:22-26),
 // regrouped.  A unit is the 64 int8 values one lane multiplies (see
 // quant_units.cuh) followed by 16 bytes of padding: with a stride of 80 bytes
@@ -32,18 +34,23 @@ __host__ __device__ constexpr int block_bytes(int type) {
 //   planar: u = 4b + 2n + h holds elements 256b + 128n + 32j + 16h + i at byte 16j + i.
 // ---------------------------------------------------------------------------
 constexpr int Q8_UNIT_STRIDE = 80;
+constexpr int Q8_BLOCK_STRIDE = 4 * Q8_UNIT_STRIDE + 16 + 32;   // 368
+constexpr int Q8_BLOCK_D = 4 * Q8_UNIT_STRIDE;                  // d of the block
+constexpr int Q8_BLOCK_BS = Q8_BLOCK_D + 16;                    // its sixteen group sums
 enum Q8Layout : int { Q8_LINEAR = 0, Q8_PLANAR = 1 };
-__host__ __device__ inline int q8row_d_off(int I) { return (I / 64) * Q8_UNIT_STRIDE; }
-__host__ __device__ inline int q8row_bs_off(int I) { return q8row_d_off(I) + (((I / QK_K) * 4 + 15) & ~15); }
-__host__ __device__ inline int q8row_stride(int I) { return q8row_bs_off(I) + (I / QK_K) * 32; }
+// byte offsets inside a packed row: unit u = 4b + sub, d and group sums of block b
+__host__ __device__ inline int q8_unit_off(int u) { return (u >> 2) * Q8_BLOCK_STRIDE + (u & 3) * Q8_UNIT_STRIDE; }
+__host__ __device__ inline int q8_d_off(int b) { return b * Q8_BLOCK_STRIDE + Q8_BLOCK_D; }
+__host__ __device__ inline int q8_bs_off(int b) { return b * Q8_BLOCK_STRIDE + Q8_BLOCK_BS; }
+__host__ __device__ inline int q8row_stride(int I) { return (I / QK_K) * Q8_BLOCK_STRIDE; }
 __host__ __device__ constexpr int q8_layout_of(int type) { return (type == Q2_K || type == Q3_K) ? Q8_PLANAR : Q8_LINEAR; }
 // byte offset inside the packed row of element e (0..255) of super-block b
 __host__ __device__ inline int q8row_elem_off(int layout, int b, int e) {
     if (layout == Q8_PLANAR) {
         const int n = e >> 7, j = (e >> 5) & 3, h = (e >> 4) & 1, i = e & 15;
-        return (4 * b + 2 * n + h) * Q8_UNIT_STRIDE + 16 * j + i;
+        return q8_unit_off(4 * b + 2 * n + h) + 16 * j + i;
     }
-    return (4 * b + (e >> 6)) * Q8_UNIT_STRIDE + (e & 63);
+    return q8_unit_off(4 * b + (e >> 6)) + (e & 63);
 }
 
 // ---------------------------------------------------------------------------
