@@ -785,9 +785,9 @@ def main():
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_source": which,
                     "avg_launch_ms": gu_ms, "bytes_per_launch": sum(gu_bytes) / LAYERS,
                     # dram__bytes_read + write of this kernel from ncu on a 1-layer capture of the same
-                    # batch: 342.9 MB read + 4.3 MB written for 342.8 MB of algorithmic bytes; traffic is
+                    # batch: 342.9 MB read + 5.0 MB written for 342.8 MB of algorithmic bytes; traffic is
                     # proportional to the distinct experts streamed, so the ratio carries over to a full launch
-                    "traffic": sum(gu_bytes) / LAYERS * (347.2 / 342.8),
+                    "traffic": sum(gu_bytes) / LAYERS * (347.9 / 342.8),
                     "traffic_source": "scaled from the ncu capture of a 1-layer run of the same batch "
                                       "(profiles/mmid2_kernel_decode_cfg2.md), not measured in this run",
                     "distinct_experts_per_layer": nact}
