@@ -30,8 +30,8 @@ static bool mmid2_geometry(int type, int I, int O, bool dual, MmidGeom *g) {
         const bool whole = cb == nb;
         const bool tiled = rb % 16 == 0 && (cb * bb) % 16 == 0;
         if (!tiled && !whole) continue;
-        // a chunk that is not the whole row needs 16-byte pieces of the packed activation row as well: slices of
-        // four super-blocks (a slice then serves two chunks of two)
+        // a chunk that is not the whole row rides with a slice of the packed activation row (stored block by block,
+        // so any run of blocks is one 16-byte-aligned piece): four super-blocks, which then cover two chunks of two
         const int acb = whole ? cb : (cb == 2 ? 4 : cb);
         if (!whole && (acb % 4 != 0 || nb % acb != 0)) continue;
         int pitch = rb;
