@@ -44,7 +44,7 @@ struct M2Params {
     int pitch;       // bytes between rows of a tile in shared memory
     int lb_log2;     // one-pair path: log2 of the lanes that share a row (one super-block each)
     int acb;         // super-blocks of the activation slice a stage holds: cb, or 4 where cb is 2 (the slice then
-                     // covers two consecutive chunks; the tensor-core path works on slices of four blocks)
+                     // covers two consecutive chunks)
     int I_l;         // elements of that slice
     int maxtok;      // pairs per item the plan was built with
     int q8s_l;       // bytes between the pairs' activation slices in shared memory
